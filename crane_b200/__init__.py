@@ -45,6 +45,11 @@ class Sampling(C.Structure):
                 ("uniforms", C.c_void_p), ("seed", C.c_uint64)]
 
 
+class StepEntry(C.Structure):
+    """`crane_b200_step_entry`: the next tokens of one sequence and the positions among them whose logits are wanted."""
+    _fields_ = [("seq", C.c_int), ("tokens", C.c_void_p), ("n_tokens", C.c_size_t), ("want", C.c_void_p), ("n_want", C.c_size_t)]
+
+
 def make_sampling(temperature=0.0, top_p=0.0, top_k=0, repetition_penalty=1.0, frequency_penalty=0.0, presence_penalty=0.0, context=(),
                   uniforms=None, seed=0):
     """-> (Sampling, keep-alive arrays)."""
@@ -84,6 +89,8 @@ _SIGNATURES = {
     "crane_b200_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t,
                                              C.c_void_p, C.POINTER(C.c_size_t)]),
     "crane_b200_seq_create": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
+    "crane_b200_step_batch": (C.c_int, [C.c_void_p, C.POINTER(StepEntry), C.c_size_t, C.POINTER(Logits)]),
+    "crane_b200_seq_len": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_size_t)]),
     "crane_b200_kv_export": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
     "crane_b200_kv_import": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t]),
     "crane_b200_kv_set_len": (C.c_int, [C.c_void_p, C.c_size_t, C.c_uint32]),
@@ -361,6 +368,30 @@ class Engine:
     def seq_select(self, seq: int):
         self._ck(self.lib.crane_b200_seq_select(self.h, seq))
 
+    def step_batch(self, entries, copy: bool = True):
+        """One engine iteration over a ragged batch: entries = [(seq, tokens, want)], every entry the next tokens of one sequence
+        (a prompt portion or one decoded token) and the indices among them whose logits are wanted.  -> logits [sum(want), vocab]
+        in the order of the entries and of `want` (None when nothing is wanted or copy is False: they stay on the device)."""
+        keep, arr, rows = [], (StepEntry * len(entries))(), 0
+        for i, (seq, tokens, want) in enumerate(entries):
+            t = np.ascontiguousarray(tokens, dtype=np.uint32)
+            w = np.ascontiguousarray(want, dtype=np.uint32)
+            keep += [t, w]
+            arr[i] = StepEntry(int(seq), t.ctypes.data, t.size, w.ctypes.data if w.size else None, w.size)
+            rows += w.size
+        lg = Logits()
+        self._ck(self.lib.crane_b200_step_batch(self.h, arr, len(entries), C.byref(lg)))
+        if not rows or not copy:
+            return None
+        out = np.empty((rows, self.vocab), dtype=np.float32)
+        self._ck(self.lib.crane_b200_copy_logits(self.h, _ptr(out), out.size))
+        return out
+
+    def seq_len(self, seq: int) -> int:
+        n = C.c_size_t()
+        self._ck(self.lib.crane_b200_seq_len(self.h, seq, C.byref(n)))
+        return int(n.value)
+
     def decode_batch(self, seqs, tokens, n_steps: int = 1, want_logits: bool = False):
         """`step_batch_decode` x n_steps for the listed sequences -> (tokens [n, n_steps], logits [n, V] of the last round | None)."""
         sq = np.ascontiguousarray(seqs, dtype=np.int32)
@@ -578,6 +609,39 @@ class Qwen3TTSModel(Engine):
                                                   _ptr(frames), C.byref(n), None if fl is None else _ptr(fl), None if gl is None else _ptr(gl)))
         k = int(n.value)
         return (frames[:k], fl[:k], gl[:k]) if want_logits else frames[:k]
+
+
+class FosovikModel(Qwen3Model):
+    """A layer-list decoder ("architecture": "Fosovik"): each layer one Dynamic-Tanh norm feeding a token mixer (sink attention or
+    Mamba-2) and a feed-forward (clamped gated unit or mixture of experts) in parallel.  It runs ragged-batch steps natively
+    (`step_batch`); `forward_step`, `generate`, `decode_batch` and the samplers work as for the other families.
+    Engine options: max_tokens (page pool), max_batch (sequence slots), precision ("split", "bf16", "f32")."""
+
+
+# config.json -> model class, as `model_factory::create_backend` picks a backend by architecture (crane-serve/src/engine/model_factory.rs:471-560)
+def model_class(config: dict):
+    if config.get("architecture") == "Fosovik":
+        return FosovikModel
+    if "talker_config" in config:
+        return Qwen3TTSModel
+    if "vision_config" in config:
+        return Qwen3VLModel
+    tc = config.get("text_config", config)
+    return Qwen3_5Model if "linear_num_value_heads" in tc else Qwen3Model
+
+
+def load_model(model_dir: str, device: int = 0, **engine_opts):
+    """A checkpoint folder (config.json + *.safetensors) -> a finalized model of the class its config names."""
+    with open(os.path.join(model_dir, "config.json")) as f:
+        config = json.load(f)
+    m = model_class(config)(config, device=device, **engine_opts)
+    files = sorted(f for f in os.listdir(model_dir) if f.endswith(".safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no .safetensors file in {model_dir}")
+    for f in files:
+        m.load_safetensors(os.path.join(model_dir, f))
+    m.finalize()
+    return m
 
 
 def gguf_config(path: str) -> dict:

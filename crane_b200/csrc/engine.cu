@@ -24,6 +24,7 @@
 #include "json_min.h"
 #include "prefill.cuh"
 #include "quant.cuh"
+#include "ragged.cuh"
 #include "sampler.cuh"
 #include "prof.h"
 
@@ -180,6 +181,8 @@ struct MergerW {
     int loaded = 0;
 };
 
+struct FosovikModel;   // layer-list models (engine_fosovik.inc)
+
 }  // namespace
 
 #include "engine_sampler.inc"
@@ -187,6 +190,7 @@ struct MergerW {
 struct crane_b200_model {
     // ---- configuration ----
     int device = 0, num_sms = 148;
+    FosovikModel* fsv = nullptr;            // "architecture": "Fosovik" -- the handle then runs ragged-batch steps (engine_fosovik.inc)
     bool is_vl = false;
     int V = 0, H = 0, I = 0, L = 0, nh = 0, nkv = 0, D = 0;
     float eps = 1e-6f;
@@ -406,6 +410,9 @@ struct crane_b200_model {
     bool load_text_tensor(const std::string& n, int dt, const int64_t* shape, int ndim, const void* data);
     bool load_vision_tensor(const std::string& n, int dt, const int64_t* shape, int ndim, const void* data);
     void finalize();
+    void fsv_finalize();
+    void fsv_step(const crane_b200_step_entry* entries, size_t n);   // ragged-batch step of a layer-list model
+    uint32_t fsv_greedy_rows(size_t rows, uint32_t* out);             // argmax of the last step's logits rows
     void ensure_prefill_ws(int S);
     void ensure_vision_ws(int N);
 
@@ -647,6 +654,8 @@ static void want_shape(const std::string& name, const int64_t* shape, int ndim, 
     }
 }
 
+#include "engine_fosovik.inc"
+
 bool crane_b200_model::load_text_tensor(const std::string& n, int dt, const int64_t* shape, int ndim, const void* data) {
     if (n == "embed_tokens.weight") {
         want_shape(n, shape, ndim, {V, H});
@@ -808,6 +817,13 @@ bool crane_b200_model::load_vision_tensor(const std::string& n, int dt, const in
 
 void crane_b200_model::load_tensor(const std::string& name_in, int dt, const int64_t* shape, int ndim, const void* data) {
     if (is_tts && name_in.rfind("talker.", 0) == 0) { tts_load(name_in, dt, shape, ndim, data); return; }
+    if (fsv) {
+        if (finalized) fail(CRANE_B200_INVALID_ARG, "load_tensor after finalize");
+        if (dt < 0 || dt > 2) fail(CRANE_B200_INVALID_ARG, "tensor %s: unknown dtype %d", name_in.c_str(), dt);
+        CUDA_OK(cudaSetDevice(device));
+        fsv->load(name_in, dt, shape, ndim, data);
+        return;
+    }
     const std::string name = gguf_to_hf(name_in);
     struct Flag { bool& f; ~Flag() { f = false; } } flag_reset{tensor_gguf_named};
     tensor_gguf_named = name != name_in;
@@ -1010,6 +1026,7 @@ void crane_b200_model::qlinear_rows(int epi, const unsigned char* qw, int qt, in
 void crane_b200_model::finalize() {
     if (finalized) return;
     CUDA_OK(cudaSetDevice(device));
+    if (fsv) { fsv_finalize(); return; }
     if (!got_embed) fail(CRANE_B200_NOT_LOADED, "missing tensor embed_tokens.weight");
     if (!got_final_norm) fail(CRANE_B200_NOT_LOADED, "missing tensor norm.weight");
     if (!tied && !got_lm_head) fail(CRANE_B200_NOT_LOADED, "missing tensor lm_head.weight");
@@ -1759,6 +1776,35 @@ void crane_b200_model::encode_images(const float* pv, const uint32_t* grid, size
     spans.mark(SP_OTHER);                          // the pass goes on into prefill(); a bare encode_images call closes it itself
 }
 
+
+// =================================================================================================
+// layer-list models: the handle-level glue around FosovikModel::step
+// =================================================================================================
+void crane_b200_model::fsv_finalize() {
+    fsv->finalize();
+    seq_kv.assign(max_batch, 0); seq_pos.assign(max_batch, 0); seq_used.assign(max_batch, 0);
+    seq_used[0] = 1;
+    CUDA_OK(cudaMallocHost((void**)&h_tokens, sizeof(uint32_t) * out_cap));
+    CUDA_OK(cudaEventCreate(&pev0)); CUDA_OK(cudaEventCreate(&pev1)); CUDA_OK(cudaEventCreate(&dev0)); CUDA_OK(cudaEventCreate(&dev1));
+    finalized = true;
+}
+void crane_b200_model::fsv_step(const crane_b200_step_entry* entries, size_t n) {
+    std::vector<FosovikModel::Entry> es(n);
+    for (size_t i = 0; i < n; ++i) es[i] = FosovikModel::Entry{entries[i].seq, entries[i].tokens, entries[i].n_tokens, entries[i].want, entries[i].n_want};
+    fsv->step(es.data(), n);
+    logits = fsv->logits;
+    launches = fsv->launches;
+    kv_len = (size_t)fsv->seqs[cur].len;
+    for (int i = 0; i < max_batch; ++i) { seq_kv[i] = (size_t)fsv->seqs[i].len; seq_used[i] = fsv->seqs[i].used; }
+}
+// greedy tokens of the first `rows` logits rows of the last step (sampler's argmax: lowest index among maxima)
+uint32_t crane_b200_model::fsv_greedy_rows(size_t rows, uint32_t* out) {
+    std::vector<crane_b200_sampling> g(rows);
+    for (auto& p : g) { p = crane_b200_sampling{}; p.repetition_penalty = 1.f; }
+    sampler_run(stream, sampler, fsv->logits, V, rows, g.data(), out);
+    return out[0];
+}
+
 // =================================================================================================
 // C ABI
 // =================================================================================================
@@ -1784,7 +1830,11 @@ static void need_ready(crane_b200_model* m) {
 static void fill_logits(crane_b200_model* m, crane_b200_logits* out) {
     if (out) { out->device_ptr = m->logits; out->rows = 1; out->vocab = (size_t)m->V; out->stream = (void*)m->stream; }
 }
+static void dense_only(crane_b200_model* m, const char* what) {
+    if (m->fsv) fail(CRANE_B200_UNSUPPORTED, "%s is not available on a layer-list model (use step_batch / forward_step / decode_batch)", what);
+}
 static void check_room(crane_b200_model* m, size_t start_pos, size_t n) {
+    if (m->fsv) { if (start_pos != m->kv_len) fail(CRANE_B200_INVALID_ARG, "start_pos %zu != cached length %zu", start_pos, m->kv_len); return; }
     if (start_pos != m->kv_len) fail(CRANE_B200_INVALID_ARG, "start_pos %zu != cached length %zu", start_pos, m->kv_len);
     if (start_pos + n > (size_t)m->max_seq) fail(CRANE_B200_OOM, "sequence length %zu exceeds max_seq_len %d", start_pos + n, m->max_seq);
 }
@@ -1807,6 +1857,20 @@ int crane_b200_create(const char* config_json, int device_ordinal, crane_b200_mo
         CUDA_OK(cudaGetDeviceProperties(&prop, device_ordinal));
         if (prop.major != 10) fail(CRANE_B200_UNSUPPORTED, "device %s is sm_%d%d; this library is built for sm_100a only", prop.name, prop.major, prop.minor);
         m->num_sms = prop.multiProcessorCount;
+        {
+            cbjson::Value root = cbjson::Parser(config_json).parse();
+            if (root.type == cbjson::Value::OBJ && root.string("architecture", "") == "Fosovik") {
+                m->fsv = new FosovikModel();
+                m->fsv->device = device_ordinal; m->fsv->num_sms = m->num_sms;
+                m->fsv->parse(root);
+                m->V = m->fsv->V; m->H = m->fsv->W; m->L = (int)m->fsv->layers.size(); m->max_batch = m->fsv->max_batch;
+                m->use_persistent = false;
+                CUDA_OK(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+                m->fsv->stream = m->stream;
+                *out = m.release();
+                return CRANE_B200_OK;
+            }
+        }
         m->parse_config(config_json);
         CUDA_OK(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
         m->alloc_weights();
@@ -1823,10 +1887,12 @@ int crane_b200_create(const char* config_json, int device_ordinal, crane_b200_mo
     } catch (const EngineError& e) {
         g_create_error = e.msg;
         for (void* p : m->allocs) cudaFree(p);
+        if (m->fsv) { m->fsv->release(); delete m->fsv; }
         return e.code;
     } catch (const std::exception& e) {
         g_create_error = e.what();
         for (void* p : m->allocs) cudaFree(p);
+        if (m->fsv) { m->fsv->release(); delete m->fsv; }
         return CRANE_B200_INVALID_ARG;
     }
     *out = m.release();
@@ -1843,6 +1909,7 @@ void crane_b200_destroy(crane_b200_model* m) {
     if (m->cp) { crane_b200_destroy(m->cp); m->cp = nullptr; }
     for (auto& ga : m->graph_step) for (auto& g : ga) if (g) cudaGraphExecDestroy(g);
     for (void* p : m->allocs) cudaFree(p);
+    if (m->fsv) { m->fsv->release(); delete m->fsv; m->fsv = nullptr; }
     if (m->h_state_ring) cudaFreeHost(m->h_state_ring);
     for (cudaEvent_t e : m->h_state_ev) if (e) cudaEventDestroy(e);
     if (m->h_tokens) cudaFreeHost(m->h_tokens);
@@ -1888,7 +1955,11 @@ int crane_b200_forward_step(crane_b200_model* m, const uint32_t* ids, size_t n, 
     check_room(m, start_pos, n);
     for (size_t i = 0; i < n; ++i)
         if (ids[i] >= (uint32_t)m->V) fail(CRANE_B200_INVALID_ARG, "token id %u >= vocab %d", ids[i], m->V);
-    if (n == 1) {
+    if (m->fsv) {              // one entry: the current sequence, logits of its last row
+        const uint32_t last = (uint32_t)(n - 1);
+        const crane_b200_step_entry e{m->cur, ids, n, &last, 1};
+        m->fsv_step(&e, 1);
+    } else if (n == 1) {
         CUDA_OK(cudaEventRecord(m->dev0, m->stream));
         m->arm_state(ids[0], start_pos, (int)start_pos, (int)start_pos, (int)start_pos);
         m->embed_step_input(1);
@@ -1910,6 +1981,7 @@ int crane_b200_forward_step_argmax(crane_b200_model* m, const uint32_t* ids, siz
     int r = crane_b200_forward_step(m, ids, n, start_pos, nullptr);
     if (r != CRANE_B200_OK) return r;
     API_BEGIN(m)
+    if (m->fsv) { m->fsv_greedy_rows(1, token_out); return CRANE_B200_OK; }
     CUDA_OK(cudaMemcpyAsync(m->h_tokens, m->out_tokens, sizeof(uint32_t), cudaMemcpyDeviceToHost, m->stream));
     m->ll_err_fetch();
     CUDA_OK(cudaStreamSynchronize(m->stream));
@@ -1920,6 +1992,7 @@ int crane_b200_forward_step_argmax(crane_b200_model* m, const uint32_t* ids, siz
 
 int crane_b200_clear_kv_cache(crane_b200_model* m) {
     API_BEGIN(m)
+    if (m->fsv && m->finalized) m->fsv->seq_free(m->cur);     // pages back to the pool, recurrent state zeroed; the slot stays
     m->kv_len = 0;
     m->next_mrope_pos = 0;
     if (m->finalized && m->hybrid) m->reset_recurrent_state();
@@ -1933,6 +2006,7 @@ size_t crane_b200_kv_len(const crane_b200_model* m) { return m ? m->kv_len : 0; 
 uint32_t crane_b200_next_mrope_pos(const crane_b200_model* m) { return m ? m->next_mrope_pos : 0; }
 uint64_t crane_b200_active_kv_cache_bytes(const crane_b200_model* m) {
     if (!m) return 0;
+    if (m->fsv) return m->fsv->active_bytes();
     uint64_t full = 0;
     for (int f : m->layer_is_full) full += f;
     const uint64_t per_row = m->kv_bits ? (uint64_t)m->D * m->kv_bits / 8 + 4 /*codes + f32 scale*/ : (uint64_t)m->D * (m->split ? 4 : 2) /*bf16 (+ lo plane)*/;
@@ -1961,6 +2035,17 @@ int crane_b200_warmup(crane_b200_model* m) {
     const size_t saved = m->kv_len;
     const uint32_t saved_pos = m->next_mrope_pos;
     if (saved != 0) fail(CRANE_B200_INVALID_ARG, "warmup requires an empty KV cache");
+    if (m->fsv) {
+        const uint32_t w_ids[4] = {0, 1 % (uint32_t)m->V, 2 % (uint32_t)m->V, 3 % (uint32_t)m->V}, last = 3, zero = 0;
+        crane_b200_step_entry e{m->cur, w_ids, 4, &last, 1};
+        m->fsv_step(&e, 1);
+        e = crane_b200_step_entry{m->cur, w_ids, 1, &zero, 1};
+        m->fsv_step(&e, 1);
+        CUDA_OK(cudaStreamSynchronize(m->stream));
+        m->fsv->seq_free(m->cur);
+        m->kv_len = 0;
+        return CRANE_B200_OK;
+    }
     uint32_t ids[4] = {0, 1 % (uint32_t)m->V, 2 % (uint32_t)m->V, 3 % (uint32_t)m->V};
     m->prefill(ids, nullptr, 4, nullptr, 0, nullptr, 0, 1);
     m->decode_steps(2, 1);
@@ -1975,7 +2060,7 @@ int crane_b200_warmup(crane_b200_model* m) {
 int crane_b200_copy_logits(crane_b200_model* m, float* host_out, size_t n_floats) {
     API_BEGIN(m)
     need_ready(m);
-    if (!host_out || n_floats > (size_t)m->V) fail(CRANE_B200_INVALID_ARG, "copy_logits: bad arguments");
+    if (!host_out || n_floats > (size_t)m->V * (m->fsv ? (size_t)std::max(m->fsv->n_rows_out, 1) : 1)) fail(CRANE_B200_INVALID_ARG, "copy_logits: bad arguments");
     CUDA_OK(cudaMemcpyAsync(host_out, m->logits, n_floats * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
     m->ll_err_fetch();
     CUDA_OK(cudaStreamSynchronize(m->stream));
@@ -1987,6 +2072,7 @@ int crane_b200_forward_embeds(crane_b200_model* m, const float* embeds, size_t s
                               crane_b200_logits* out) {
     API_BEGIN(m)
     need_ready(m);
+    dense_only(m, "forward_embeds");
     if (!embeds || s == 0) fail(CRANE_B200_INVALID_ARG, "forward_embeds: empty input");
     check_room(m, start_pos, s);
     uint32_t nxt = (uint32_t)(start_pos + s);
@@ -2009,6 +2095,25 @@ int crane_b200_decode_greedy(crane_b200_model* m, uint32_t first_token, size_t s
     if (n_steps > (size_t)m->out_cap) fail(CRANE_B200_INVALID_ARG, "decode_greedy: n_steps %zu > %d", n_steps, m->out_cap);
     if (first_token >= (uint32_t)m->V) fail(CRANE_B200_INVALID_ARG, "token id %u >= vocab %d", first_token, m->V);
     check_room(m, start_pos, n_steps);
+    if (m->fsv) {             // one ragged step per token; the argmax stays on the device until the 4-byte read
+        uint32_t tok = first_token;
+        const uint32_t zero = 0;
+        size_t cnt = 0;
+        CUDA_OK(cudaEventRecord(m->dev0, m->stream));
+        for (size_t i = 0; i < n_steps; ++i) {
+            const crane_b200_step_entry e{m->cur, &tok, 1, &zero, 1};
+            m->fsv_step(&e, 1);
+            m->fsv_greedy_rows(1, &tok);
+            tokens_out[cnt++] = tok;
+            bool stop = false;
+            for (size_t k = 0; k < n_eos; ++k) stop = stop || (eos_ids && tok == eos_ids[k]);
+            if (stop) break;
+        }
+        CUDA_OK(cudaEventRecord(m->dev1, m->stream));
+        m->last_decode_steps = cnt;
+        *n_out = cnt;
+        return CRANE_B200_OK;
+    }
     CUDA_OK(cudaEventRecord(m->dev0, m->stream));
     const int p = (int)m->next_mrope_pos;
     m->arm_state(first_token, start_pos, p, p, p);
@@ -2057,6 +2162,7 @@ int crane_b200_encode_images(crane_b200_model* m, const float* pixel_values, con
                              float* deepstack_out) {
     API_BEGIN(m)
     need_ready(m);
+    dense_only(m, "encode_images");
     if (!pixel_values || !grid_thw || n_images == 0) fail(CRANE_B200_INVALID_ARG, "encode_images: bad arguments");
     m->encode_images(pixel_values, grid_thw, n_images);
     m->spans.end((size_t)m->img_tokens * m->v_merge * m->v_merge, 1);
@@ -2072,6 +2178,7 @@ int crane_b200_vl_forward(crane_b200_model* m, const uint32_t* ids, size_t n, co
                           size_t n_images, size_t start_pos, crane_b200_logits* out) {
     API_BEGIN(m)
     need_ready(m);
+    dense_only(m, "vl_forward");
     if (!m->is_vl) fail(CRANE_B200_UNSUPPORTED, "vl_forward on a text-only model");
     if (!ids || n == 0) fail(CRANE_B200_INVALID_ARG, "vl_forward: empty input");
     check_room(m, start_pos, n);
@@ -2131,6 +2238,7 @@ int crane_b200_vl_forward(crane_b200_model* m, const uint32_t* ids, size_t n, co
 int crane_b200_vl_decode_step(crane_b200_model* m, uint32_t token, size_t start_pos, crane_b200_logits* out) {
     API_BEGIN(m)
     need_ready(m);
+    dense_only(m, "vl_decode_step");
     if (token >= (uint32_t)m->V) fail(CRANE_B200_INVALID_ARG, "token id %u >= vocab %d", token, m->V);
     check_room(m, start_pos, 1);
     const int p = (int)m->next_mrope_pos;
@@ -2162,6 +2270,7 @@ int crane_b200_seq_create(crane_b200_model* m, int* seq_out) {
     API_BEGIN(m)
     need_ready(m);
     if (!seq_out) fail(CRANE_B200_INVALID_ARG, "seq_create: null output");
+    if (m->fsv) { *seq_out = m->fsv->seq_create(); m->seq_used[*seq_out] = 1; m->seq_kv[*seq_out] = 0; return CRANE_B200_OK; }
     int s = -1;
     for (int i = 0; i < m->max_batch; ++i)
         if (!m->seq_used[i]) { s = i; break; }
@@ -2185,6 +2294,7 @@ int crane_b200_seq_create(crane_b200_model* m, int* seq_out) {
 int crane_b200_kv_export(crane_b200_model* m, int layer, float* k_out, float* v_out, size_t capacity_floats, size_t* n_tokens) {
     API_BEGIN(m)
     need_ready(m);
+    dense_only(m, "kv_export");
     if (layer < 0 || layer >= m->L || !n_tokens) fail(CRANE_B200_INVALID_ARG, "kv_export: bad layer %d", layer);
     LayerW& l = m->layers[layer];
     const size_t T = m->kv_len;
@@ -2223,6 +2333,7 @@ int crane_b200_kv_export(crane_b200_model* m, int layer, float* k_out, float* v_
 int crane_b200_kv_import(crane_b200_model* m, int layer, const float* k, const float* v, size_t n_tokens) {
     API_BEGIN(m)
     need_ready(m);
+    dense_only(m, "kv_import");
     if (layer < 0 || layer >= m->L || !k || !v) fail(CRANE_B200_INVALID_ARG, "kv_import: bad arguments (layer %d)", layer);
     LayerW& l = m->layers[layer];
     if (!l.full) {
@@ -2256,6 +2367,7 @@ int crane_b200_kv_import(crane_b200_model* m, int layer, const float* k, const f
 int crane_b200_kv_set_len(crane_b200_model* m, size_t n_tokens, uint32_t next_rotary_pos) {
     API_BEGIN(m)
     need_ready(m);
+    dense_only(m, "kv_set_len");
     if (n_tokens > (size_t)m->max_seq) fail(CRANE_B200_OOM, "kv_set_len: %zu exceeds max_seq_len %d", n_tokens, m->max_seq);
     m->kv_len = n_tokens;
     m->next_mrope_pos = next_rotary_pos;
@@ -2265,6 +2377,7 @@ int crane_b200_kv_set_len(crane_b200_model* m, size_t n_tokens, uint32_t next_ro
 int crane_b200_seq_fork(crane_b200_model* m, int src, int* seq_out) {
     API_BEGIN(m)
     need_ready(m);
+    dense_only(m, "seq_fork");
     if (!seq_out) fail(CRANE_B200_INVALID_ARG, "seq_fork: null output");
     if (src < 0 || src >= m->max_batch || !m->seq_used[src]) fail(CRANE_B200_INVALID_ARG, "seq_fork: bad sequence %d", src);
     int s = -1;
@@ -2282,6 +2395,12 @@ int crane_b200_seq_free(crane_b200_model* m, int seq) {
     need_ready(m);
     if (seq < 0 || seq >= m->max_batch || !m->seq_used[seq]) fail(CRANE_B200_INVALID_ARG, "seq_free: bad sequence %d", seq);
     if (seq == 0) fail(CRANE_B200_INVALID_ARG, "sequence 0 is the handle's implicit sequence (use clear_kv_cache)");
+    if (m->fsv) {
+        m->fsv->seq_free(seq);
+        m->seq_used[seq] = 0; m->seq_kv[seq] = 0;
+        if (m->cur == seq) { m->cur = 0; m->kv_len = (size_t)m->fsv->seqs[0].len; }
+        return CRANE_B200_OK;
+    }
     m->select_seq(0);
     m->seq_used[seq] = 0;
     m->seq_kv[seq] = 0; m->seq_pos[seq] = 0;
@@ -2292,6 +2411,7 @@ int crane_b200_seq_select(crane_b200_model* m, int seq) {
     API_BEGIN(m)
     need_ready(m);
     if (seq < 0 || seq >= m->max_batch || !m->seq_used[seq]) fail(CRANE_B200_INVALID_ARG, "seq_select: bad sequence %d", seq);
+    if (m->fsv) { m->cur = seq; m->kv_len = (size_t)m->fsv->seqs[seq].len; return CRANE_B200_OK; }   // state lives in its slot: nothing to swap
     m->select_seq(seq);
     API_END(m)
 }
@@ -2302,6 +2422,21 @@ int crane_b200_decode_batch(crane_b200_model* m, const int* seqs, const uint32_t
     need_ready(m);
     if (!seqs || !tokens || !tokens_out || n == 0 || n_steps == 0) fail(CRANE_B200_INVALID_ARG, "decode_batch: bad arguments");
     if (m->hybrid) fail(CRANE_B200_UNSUPPORTED, "decode_batch on the hybrid model");
+    if (m->fsv) {             // every round is one ragged step of n single-token entries
+        std::vector<uint32_t> cur_tok(tokens, tokens + n), next(n);
+        std::vector<crane_b200_step_entry> es(n);
+        const uint32_t zero = 0;
+        for (size_t t = 0; t < n_steps; ++t) {
+            for (size_t i = 0; i < n; ++i) es[i] = crane_b200_step_entry{seqs[i], &cur_tok[i], 1, &zero, 1};
+            m->fsv_step(es.data(), n);
+            if (logits_host && t + 1 == n_steps)
+                CUDA_OK(cudaMemcpyAsync(logits_host, m->logits, n * (size_t)m->V * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
+            m->fsv_greedy_rows(n, next.data());
+            for (size_t i = 0; i < n; ++i) { tokens_out[i * n_steps + t] = next[i]; cur_tok[i] = next[i]; }
+        }
+        m->last_decode_steps = n_steps;
+        return CRANE_B200_OK;
+    }
     if (n_steps > (size_t)m->out_cap) fail(CRANE_B200_INVALID_ARG, "decode_batch: n_steps %zu > %d", n_steps, m->out_cap);
     m->seq_kv[m->cur] = m->kv_len; m->seq_pos[m->cur] = m->next_mrope_pos;
     for (size_t i = 0; i < n; ++i) {
@@ -2351,6 +2486,24 @@ int crane_b200_decode_batch(crane_b200_model* m, const int* seqs, const uint32_t
     API_END(m)
 }
 
+// ---- ragged-batch step: the scheduler's decision for one engine iteration, run as one batch ----
+int crane_b200_step_batch(crane_b200_model* m, const crane_b200_step_entry* entries, size_t n_entries, crane_b200_logits* out) {
+    API_BEGIN(m)
+    need_ready(m);
+    if (!entries || n_entries == 0) fail(CRANE_B200_INVALID_ARG, "step_batch: no entries");
+    for (size_t i = 0; i < n_entries; ++i)
+        if (entries[i].n_want && !entries[i].want) fail(CRANE_B200_INVALID_ARG, "step_batch: entry %zu: n_want without want", i);
+    if (!m->fsv) fail(CRANE_B200_UNSUPPORTED, "step_batch: this model family runs one sequence per prefill call (forward_step) and decode_batch");
+    m->fsv_step(entries, n_entries);
+    if (out) { out->device_ptr = m->logits; out->rows = (size_t)m->fsv->n_rows_out; out->vocab = (size_t)m->V; out->stream = (void*)m->stream; }
+    API_END(m)
+}
+int crane_b200_seq_len(const crane_b200_model* m, int seq, size_t* len_out) {
+    if (!m || !m->finalized || !len_out || seq < 0 || seq >= m->max_batch) return CRANE_B200_INVALID_ARG;
+    *len_out = m->fsv ? (size_t)m->fsv->seqs[seq].len : (seq == m->cur ? m->kv_len : m->seq_kv[seq]);
+    return CRANE_B200_OK;
+}
+
 // ---- device-side sampling (crane-serve/src/engine/sampling.rs:169-480) ----
 int crane_b200_sample(crane_b200_model* m, const crane_b200_sampling* p, uint32_t* token_out) {
     API_BEGIN(m)
@@ -2388,6 +2541,14 @@ int crane_b200_decode_batch_sample(crane_b200_model* m, const int* seqs, const u
     need_ready(m);
     if (!seqs || !tokens || !tokens_out || !params || n == 0) fail(CRANE_B200_INVALID_ARG, "decode_batch_sample: bad arguments");
     if (m->hybrid) fail(CRANE_B200_UNSUPPORTED, "decode_batch_sample on the hybrid model");
+    if (m->fsv) {
+        std::vector<crane_b200_step_entry> es(n);
+        const uint32_t zero = 0;
+        for (size_t i = 0; i < n; ++i) es[i] = crane_b200_step_entry{seqs[i], &tokens[i], 1, &zero, 1};
+        m->fsv_step(es.data(), n);
+        sampler_run(m->stream, m->sampler, m->logits, m->V, n, params, tokens_out);
+        return CRANE_B200_OK;
+    }
     m->seq_kv[m->cur] = m->kv_len; m->seq_pos[m->cur] = m->next_mrope_pos;
     for (size_t i = 0; i < n; ++i) {
         const int s = seqs[i];

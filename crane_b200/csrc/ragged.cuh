@@ -1,0 +1,103 @@
+// Kernels for models that run a RAGGED BATCH per step: the rows of one step are portions of several sequences (a prompt
+// chunk of one beside single decoded tokens of others), concatenated, with per-row and per-entry descriptors in device memory.
+// Every mechanism takes its constants as arguments so that any layer-list model can be assembled from them:
+//   Dynamic-Tanh norm, unit-RMS QK norm with a position-dependent query temperature, paged softmax attention with a sink term
+//   (any key width, any value width, grouped queries, keys / values optionally owned by another layer), the Mamba-2 mixer
+//   (causal depthwise convolution with carried window, selective state-space scan with carried f32 state, gated grouped RMS
+//   norm), a clamped gated feed-forward, and a softmax-routed mixture of experts (router, counting sort, grouped linears,
+//   ordered combine).  See ragged.cu.
+#pragma once
+
+#include "common.cuh"
+
+namespace cb {
+
+struct RaggedBatch {
+    const int* row_entry;   // [T] entry of each row
+    const int* row_pos;     // [T] position of each row in its sequence (0-based)
+    const int* ent_row0;    // [E] first row of the entry
+    const int* ent_len;     // [E] rows of the entry
+    const int* ent_pos0;    // [E] tokens the sequence held before this step
+    const int* ent_slot;    // [E] sequence slot: block-table row and recurrent-state slot
+    int T, E;
+};
+
+// An activation buffer as the linears read it: f32 rows (exact mode, routers) and / or bf16 planes hi (+ lo at an element offset).
+struct ActOut {
+    float* f = nullptr; int ldf = 0;
+    bf16* hi = nullptr; long long lo_off = 0; int ldb = 0;
+};
+
+enum LinearMode : int { LIN_STORE = 0, LIN_RESID = 1 };
+
+int embed_scale_rows_launch(cudaStream_t st, const int* ids, int T, const bf16* embed, int W, float scale, float* x, int ldx);
+// out[r, c] = tanh(alpha * x[src(r), c]) * w[c] + b[c];  rows = gather list (nullptr: identity)
+int dyt_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, const float* alpha, const float* w,
+                    const float* b, const ActOut& out);
+// C[M, N] (+)= A[M, K] f32 x W[N, K]^T bf16, every product and sum in f32 (no tensor cores): the exact mode's linear, and the router's
+int linear_f32_launch(cudaStream_t st, const float* A, int lda, const bf16* W, int ldw, int M, int N, int K, int mode, float* C, int ldc);
+
+struct AttnPrepArgs {
+    const float* qkv; int ld;         // [T, ld]: q heads | k heads | v heads (k / v absent when has_kv == 0)
+    int H, G, d, dv;
+    float eps;
+    float temp_coef; int temp_every;  // temp_every <= 0: no query temperature
+    float* q_out; int ldq;            // [T, H * d] normalised, temperature applied
+    void* k_pool; void* v_pool;       // pages [n_pages, G, KV_PAGE, d | dv] of f32 or bf16
+    int kv_f32;
+    int has_kv;
+    const int* block_table; int max_pages;
+};
+int attn_prep_launch(cudaStream_t st, const RaggedBatch& rb, const AttnPrepArgs& a);
+
+struct SinkAttnArgs {
+    const float* q; int ldq;          // [T, H * d]
+    const void* k_pool; const void* v_pool; int kv_f32;
+    const int* block_table; int max_pages;
+    int H, G, d, dv;
+    float scale;
+    const float* sink;                // [H] or nullptr (no sink term)
+    ActOut out;                       // [T, H * dv]
+    float* part; int nsplit;          // scratch [T, H, nsplit, dv + 2] when nsplit > 1
+};
+int sink_attention_launch(cudaStream_t st, const RaggedBatch& rb, const SinkAttnArgs& a);
+
+struct Mamba2Args {
+    const float* proj; int ldp;       // [T, ldp]: z | x | B | C | dt
+    int heads, P, N, groups, taps, norm_groups;
+    const float* conv_w;              // [C, taps], C = heads * P + 2 * groups * N
+    const float* conv_b;              // [C]
+    const float* dt_bias; const float* A_log; const float* D;   // [heads]
+    const float* norm_w;              // [heads * P]
+    float eps;
+    float* conv_state;                // [slots, taps - 1, C] the inputs before the next token
+    float* ssm_state;                 // [slots, heads, N, P] f32
+    float* xbc;                       // [T, C] scratch: conv + silu
+    float* y;                         // [T, heads * P] scratch
+    ActOut out;                       // gated, normalised [T, heads * P]
+};
+int mamba2_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba2Args& a);
+int mamba2_launch_count();
+
+// out[r, j] = g * sigmoid(1.702 g) * (u + 1),  g = min(gu[r, j], limit),  u = clamp(gu[r, up_off + j], -limit, limit)
+int clamped_glu_launch(cudaStream_t st, const float* gu, int ld, int up_off, int T, int F, float limit, const ActOut& out);
+
+struct MoeArgs {
+    int T, E, top, F, W;              // rows, experts, experts per row, expert width, model width
+    const float* h; int ldh;          // [T, ldh] f32 input rows
+    const float* router_logits; int ldr;   // [T, ldr]
+    const bf16* const* up;            // [E] device pointers, each [F, ldwu]
+    const bf16* const* down;          // [E] each [W, ldwd]
+    int ldwu, ldwd;
+    int* sel_e; float* sel_w;         // [T * top]
+    int* sorted; int* tile_e; int* tile_r0; int* tile_n; int* n_tiles; int max_tiles;
+    float* act; int lda;              // [T * top, lda]
+    float* y; int ldy;                // [T * top, ldy]
+    float* x; int ldx;                // residual, += sum_k w_k y_k
+};
+int moe_launch(cudaStream_t st, const MoeArgs& a);
+inline int moe_max_tiles(int T, int top, int E) { return (T * top + 31) / 32 + E; }
+
+int gather_rows_launch(cudaStream_t st, const float* src, int lds, const int* rows, int R, int W, float* dst, int ldd);
+
+}  // namespace cb

@@ -186,6 +186,26 @@ CRANE_B200_API int crane_b200_seq_select(crane_b200_model* m, int seq);
 CRANE_B200_API int crane_b200_decode_batch(crane_b200_model* m, const int* seqs, const uint32_t* tokens, size_t n, size_t n_steps,
                                            uint32_t* tokens_out, float* logits_host);
 
+/* ---- ragged-batch step (continuous batching with chunked prefill) -------------------------------------------------------------
+ * One engine iteration as the scheduler decided it (crane-serve/src/engine/mod.rs:822-1062 picks which sequences advance and by
+ * how much): every entry brings the next n_tokens of one sequence -- a portion of a prompt, cut anywhere, or one decoded token --
+ * and all entries run as ONE batch over the weights, each sequence on its own KV pages and recurrent-state slot.  `want` lists the
+ * positions among an entry's tokens whose logits are computed; the result rows follow the order of the entries and of `want`
+ * (crane_b200_copy_logits copies rows * vocab floats).  Layer-list models ("architecture" in config.json, e.g. "Fosovik") run this
+ * natively; their KV pages come from one pool of engine.max_tokens tokens (64 per page) that sequences draw from as they grow and
+ * return to with seq_free / clear_kv_cache, and engine.max_batch sequence slots hold the recurrent state.
+ * "engine": {"max_tokens": N, "max_batch": B, "precision": "split"|"bf16"|"f32"} -- "f32" runs every product in true 32-bit. */
+typedef struct {
+    int seq;                  /* slot from crane_b200_seq_create (0 = the handle's implicit sequence) */
+    const uint32_t* tokens;   /* host: the sequence's next n_tokens */
+    size_t n_tokens;
+    const uint32_t* want;     /* host: indices into tokens (may be NULL when n_want == 0) */
+    size_t n_want;
+} crane_b200_step_entry;
+CRANE_B200_API int crane_b200_step_batch(crane_b200_model* m, const crane_b200_step_entry* entries, size_t n_entries, crane_b200_logits* out);
+/* Tokens sequence `seq` holds in the cache. */
+CRANE_B200_API int crane_b200_seq_len(const crane_b200_model* m, int seq, size_t* len_out);
+
 /* ---- multi-GPU batch decode (BASELINE.json config 4: 32 sequences over 8 x B200) ----------------------------------------------
  * One process and one handle per GPU, every rank holding the full weights and its share of the sequences; the only data-path
  * exchange is the all-gather of each round's results (NCCL over NVLink, enqueued on the engine stream behind the lm_head).
