@@ -104,6 +104,7 @@ _SIGNATURES = {
     "crane_b200_decode_batch_gather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.POINTER(Logits)]),
     "crane_b200_copy_gathered_logits": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "crane_b200_sample": (C.c_int, [C.c_void_p, C.POINTER(Sampling), C.POINTER(C.c_uint32)]),
+    "crane_b200_sample_rows": (C.c_int, [C.c_void_p, C.POINTER(Sampling), C.c_size_t, C.c_void_p]),
     "crane_b200_forward_step_sample": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.POINTER(Sampling), C.POINTER(C.c_uint32)]),
     "crane_b200_decode_batch_sample": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(Sampling), C.c_void_p]),
     "crane_b200_topk": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
@@ -408,6 +409,14 @@ class Engine:
         tok = C.c_uint32()
         self._ck(self.lib.crane_b200_sample(self.h, C.byref(sp), C.byref(tok)))
         return int(tok.value)
+
+    def sample_rows(self, params):
+        """`sampling::sample` on the logits rows of the last step_batch; params = one make_sampling keyword dict per row."""
+        made = [make_sampling(**p) for p in params]
+        arr = (Sampling * len(made))(*[m[0] for m in made])
+        out = np.empty(len(made), dtype=np.uint32)
+        self._ck(self.lib.crane_b200_sample_rows(self.h, arr, len(made), _ptr(out)))
+        return out
 
     def forward_step_sample(self, ids, start_pos: int, **kw) -> int:
         ids = np.ascontiguousarray(ids, dtype=np.uint32)

@@ -2515,6 +2515,16 @@ int crane_b200_sample(crane_b200_model* m, const crane_b200_sampling* p, uint32_
     API_END(m)
 }
 
+int crane_b200_sample_rows(crane_b200_model* m, const crane_b200_sampling* params, size_t n_rows, uint32_t* tokens_out) {
+    API_BEGIN(m)
+    need_ready(m);
+    if (!params || !tokens_out || n_rows == 0) fail(CRANE_B200_INVALID_ARG, "sample_rows: bad arguments");
+    const size_t have = m->fsv ? (size_t)m->fsv->n_rows_out : 1;
+    if (n_rows > have) fail(CRANE_B200_INVALID_ARG, "sample_rows: %zu rows asked, the last call left %zu", n_rows, have);
+    sampler_run(m->stream, m->sampler, m->logits, m->V, n_rows, params, tokens_out);
+    API_END(m)
+}
+
 int crane_b200_forward_step_sample(crane_b200_model* m, const uint32_t* ids, size_t n, size_t start_pos, const crane_b200_sampling* p,
                                    uint32_t* token_out) {
     if (!p || !token_out) return CRANE_B200_INVALID_ARG;

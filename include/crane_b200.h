@@ -242,6 +242,8 @@ typedef struct {
 } crane_b200_sampling;
 /* `sampling::sample` on the logits of the LAST forward call of the current sequence (they stay on the device; 4 bytes return). */
 CRANE_B200_API int crane_b200_sample(crane_b200_model* m, const crane_b200_sampling* p, uint32_t* token_out);
+/* `sampling::sample` row by row on the first n_rows logits rows the last call left (step_batch: one row per wanted position). */
+CRANE_B200_API int crane_b200_sample_rows(crane_b200_model* m, const crane_b200_sampling* params, size_t n_rows, uint32_t* tokens_out);
 /* forward_step + sample in one call: the server's non-greedy decode step (crane-serve/src/engine/mod.rs:938-1062). */
 CRANE_B200_API int crane_b200_forward_step_sample(crane_b200_model* m, const uint32_t* input_ids, size_t n, size_t start_pos,
                                                   const crane_b200_sampling* p, uint32_t* token_out);

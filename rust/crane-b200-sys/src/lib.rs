@@ -44,6 +44,16 @@ pub struct crane_b200_sampling {
     pub seed: u64,
 }
 
+#[repr(C)]
+#[derive(Clone, Copy)]
+pub struct crane_b200_step_entry {
+    pub seq: c_int,
+    pub tokens: *const u32,
+    pub n_tokens: usize,
+    pub want: *const u32,
+    pub n_want: usize,
+}
+
 #[link(name = "crane_b200")]
 extern "C" {
     pub fn crane_b200_create(config_json: *const c_char, device_ordinal: c_int, out: *mut *mut crane_b200_model) -> c_int;
@@ -76,12 +86,15 @@ extern "C" {
     pub fn crane_b200_seq_free(m: *mut crane_b200_model, seq: c_int) -> c_int;
     pub fn crane_b200_seq_select(m: *mut crane_b200_model, seq: c_int) -> c_int;
     pub fn crane_b200_decode_batch(m: *mut crane_b200_model, seqs: *const c_int, tokens: *const u32, n: usize, n_steps: usize, tokens_out: *mut u32, logits_host: *mut f32) -> c_int;
+    pub fn crane_b200_step_batch(m: *mut crane_b200_model, entries: *const crane_b200_step_entry, n_entries: usize, out: *mut crane_b200_logits) -> c_int;
+    pub fn crane_b200_seq_len(m: *const crane_b200_model, seq: c_int, len_out: *mut usize) -> c_int;
     pub fn crane_b200_comm_unique_id(id_out: *mut u8, capacity: usize) -> c_int;
     pub fn crane_b200_comm_init(m: *mut crane_b200_model, id: *const u8, id_bytes: usize, rank: c_int, world: c_int) -> c_int;
     pub fn crane_b200_comm_world(m: *const crane_b200_model, rank_out: *mut c_int, world_out: *mut c_int) -> c_int;
     pub fn crane_b200_decode_batch_gather(m: *mut crane_b200_model, seqs: *const c_int, tokens: *const u32, n: usize, tokens_all_out: *mut u32, logits_all: *mut crane_b200_logits) -> c_int;
     pub fn crane_b200_copy_gathered_logits(m: *mut crane_b200_model, host_out: *mut f32, n_floats: usize) -> c_int;
     pub fn crane_b200_sample(m: *mut crane_b200_model, p: *const crane_b200_sampling, token_out: *mut u32) -> c_int;
+    pub fn crane_b200_sample_rows(m: *mut crane_b200_model, params: *const crane_b200_sampling, n_rows: usize, tokens_out: *mut u32) -> c_int;
     pub fn crane_b200_forward_step_sample(m: *mut crane_b200_model, input_ids: *const u32, n: usize, start_pos: usize, p: *const crane_b200_sampling, token_out: *mut u32) -> c_int;
     pub fn crane_b200_decode_batch_sample(m: *mut crane_b200_model, seqs: *const c_int, tokens: *const u32, n: usize, params: *const crane_b200_sampling, tokens_out: *mut u32) -> c_int;
     pub fn crane_b200_topk(m: *mut crane_b200_model, k: usize, idx_out: *mut u32, vals_out: *mut f32) -> c_int;

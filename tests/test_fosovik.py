@@ -1,0 +1,349 @@
+"""Fosovik (layer-list decoder on ragged-batch steps) against the plain oracle of oracle/fosovik.py.
+
+Small configurations with their own random weights; the oracle runs in float64.  The engine's "f32" precision is held to a
+tight bar (any lost key, wrong edge or stale state shows), the serving precisions to the bar their operand rounding allows.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle.fosovik import (FosovikOracle, causal_conv, dense_ff, dyt_norm, grouped_rms, moe_ff, query_temperature, random_weights,
+                            sink_attention, ssm_scan, unit_rms)
+
+# ---------------------------------------------------------------------------------------------------- configurations
+ATT = {"type": "attention", "mixer": {"heads": 8, "kv_heads": 2, "dim": 40, "vdim": 24, "scale": 0.9,
+                                      "q_temp": {"coef": 0.4, "every": 16}}, "mlp": None}
+ATT_PLAIN = {"type": "attention", "mixer": {"heads": 4, "kv_heads": 4, "dim": 18, "vdim": 36, "scale": 0.3}, "mlp": None}
+SSM = {"type": "mamba2", "mixer": {"heads": 6, "vdim": 20, "state": 24, "groups": 3, "conv": 4, "norm_groups": 2}, "mlp": None}
+SSM1 = {"type": "mamba2", "mixer": {"heads": 2, "vdim": 34, "state": 9, "groups": 1, "conv": 2, "norm_groups": 4}, "mlp": None}
+DENSE = {"kind": "dense", "ff": 200, "limit": 1.5}
+MOE = {"kind": "moe", "expert": {"ff": 48}, "router": {"experts": 6, "top": 2}}
+MOE1 = {"kind": "moe", "expert": {"ff": 40}, "router": {"experts": 5, "top": 1}}
+
+
+def layer(mixer, mlp=None, **mixer_extra):
+    m = dict(mixer["mixer"], **mixer_extra)
+    return {"type": mixer["type"], "mixer": m, "mlp": mlp}
+
+
+def config(layers, width=160, vocab=300, scale=7.0, eps=1e-5):
+    return {"architecture": "Fosovik", "vocab": vocab, "width": width, "embedding": {"scale": scale}, "norm": {"eps": eps},
+            "layers": layers}
+
+
+FULL = config([layer(ATT, MOE), layer(SSM, DENSE), layer(SSM1, MOE1), layer(ATT, None, kv_from=0), layer(ATT_PLAIN, DENSE),
+               layer(SSM, MOE)])
+SINGLE = {
+    "attention": config([layer(ATT)]),
+    "attention_plain": config([layer(ATT_PLAIN)], width=96, vocab=128),
+    "mamba2": config([layer(SSM)]),
+    "mamba2_one_group": config([layer(SSM1)], width=64, vocab=77),
+    "dense": config([layer(ATT_PLAIN, DENSE)]),
+    "moe": config([layer(ATT_PLAIN, MOE)]),
+    "moe_top1": config([layer(SSM1, MOE1)]),
+    "shared_kv": config([layer(ATT, DENSE), layer(SSM1), layer(ATT, MOE, kv_from=0)]),
+}
+
+
+def tokens(n, vocab, seed):
+    return np.random.default_rng(seed).integers(0, vocab, n).tolist()
+
+
+def rel(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+F32_TOL, SPLIT_TOL = 2e-5, 2e-3
+
+
+# ---------------------------------------------------------------------------------------------------- CPU: the oracle itself
+def test_oracle_prefill_equals_token_by_token():
+    cfg = FULL
+    o = FosovikOracle(cfg, random_weights(cfg, 1))
+    ids = tokens(41, cfg["vocab"], 2)
+    whole = o.forward(ids, o.new_state()).numpy()
+    st = o.new_state()
+    parts = [o.forward(ids[a:b], st).numpy() for a, b in ((0, 7), (7, 9), (9, 10), (10, 33), (33, 41))]
+    assert rel(np.concatenate(parts), whole) < 1e-11
+
+
+def test_oracle_mechanisms_on_known_answers():
+    # sink: one key, zero score, sink 0 -> half the value
+    q = torch.zeros(1, 1, 4, dtype=torch.float64); k = torch.ones(1, 1, 4, dtype=torch.float64); v = torch.full((1, 1, 3), 2.0, dtype=torch.float64)
+    out = sink_attention(q, k, v, torch.tensor([0]), 1.0, torch.zeros(1, dtype=torch.float64), 1)
+    assert torch.allclose(out, torch.full((1, 1, 3), 1.0, dtype=torch.float64))
+    # temperature steps every `every` positions, starting from 1
+    t = query_temperature(torch.tensor([0, 14, 15, 31]), 0.5, 16)
+    assert torch.allclose(t, torch.tensor([1.0, 1.0, 1 + 0.5 * np.log(2.0), 1 + 0.5 * np.log(3.0)], dtype=torch.float64))
+    # conv: last column is the current token's tap
+    y, win = causal_conv(torch.tensor([[1.0], [2.0], [3.0]]), torch.tensor([[10.0, 1.0]]), torch.zeros(1), torch.zeros(1, 1))
+    assert y.flatten().tolist() == [1.0, 12.0, 23.0] and win.flatten().tolist() == [3.0]
+    # scan with zero decay rate keeps everything: A_log -> -inf
+    x = torch.ones(3, 1, 2, dtype=torch.float64); B = torch.ones(3, 1, 1, dtype=torch.float64)
+    y, s = ssm_scan(x, B, B, torch.ones(3, 1, dtype=torch.float64), torch.tensor([-50.0], dtype=torch.float64), torch.zeros(1, dtype=torch.float64),
+                    torch.zeros(1, 1, 2, dtype=torch.float64), 1)
+    assert torch.allclose(y[:, 0, 0], torch.tensor([1.0, 2.0, 3.0], dtype=torch.float64))
+    assert torch.allclose(grouped_rms(torch.tensor([[3.0, 3.0, 1.0, 1.0]]), 2, 0.0), torch.ones(1, 4))
+    assert torch.allclose(unit_rms(torch.tensor([[2.0, 2.0]]), 0.0), torch.ones(1, 2))
+    assert float(dyt_norm(torch.tensor(100.0), 1.0, 2.0, 0.5)) == 2.5
+    # clamp: gate above the limit saturates, up is clamped on both sides
+    h = torch.eye(2, dtype=torch.float64)
+    out = dense_ff(h, torch.tensor([[9.0, 0.0]], dtype=torch.float64), torch.tensor([[-9.0, 9.0]], dtype=torch.float64), torch.ones(1, 1, dtype=torch.float64), 2.0)
+    g = 2.0 / (1 + np.exp(-1.702 * 2.0))
+    assert abs(float(out[0]) - g * (-2.0 + 1.0)) < 1e-12 and float(out[1]) == 0.0
+    # top-1 of two experts: weight is the softmax score itself, not 1
+    r = torch.tensor([[2.0], [0.0]], dtype=torch.float64)
+    one = [torch.ones(1, 1, dtype=torch.float64)] * 2
+    out = moe_ff(torch.ones(1, 1, dtype=torch.float64), r, one, one, 1)
+    s = np.exp(2.0) / (np.exp(2.0) + 1.0)
+    gl = 0.5 * (1 + float(torch.erf(torch.tensor(1.0 / np.sqrt(2.0)))))
+    assert abs(float(out) - s * gl) < 1e-12
+
+
+# ---------------------------------------------------------------------------------------------------- GPU
+def make(cfg, seed=0, **opts):
+    import crane_b200
+    w = random_weights(cfg, seed)
+    opts.setdefault("max_tokens", 1024)
+    opts.setdefault("max_batch", 4)
+    m = crane_b200.FosovikModel(cfg, device=0, **opts)
+    m.load_checkpoint(w.items())
+    return m, FosovikOracle(cfg, w)
+
+
+def all_rows(n):
+    return list(range(n))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(SINGLE))
+def test_each_mechanism_alone(name):
+    cfg = SINGLE[name]
+    m, o = make(cfg, 3, precision="f32")
+    ids = tokens(70, cfg["vocab"], 4)
+    got = m.step_batch([(0, ids, all_rows(70))])
+    want = o.forward(ids, o.new_state()).numpy()
+    assert rel(got, want) < F32_TOL
+    m.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("precision,tol", [("f32", F32_TOL), ("split", SPLIT_TOL)])
+def test_whole_model_prefill_and_token_by_token_decoding(precision, tol):
+    m, o = make(FULL, 5, precision=precision)
+    ids = tokens(150, FULL["vocab"], 6)
+    want = o.forward(ids, o.new_state()).numpy()
+    got = m.step_batch([(0, ids, all_rows(len(ids)))])
+    assert rel(got, want) < tol
+    m.clear_kv_cache()
+    rows = [m.step_batch([(0, ids[:3], [0, 1, 2])])]
+    rows += [m.step_batch([(0, [t], [0])]) for t in ids[3:]]       # long decoding: 147 single-token steps across two page borders
+    step = np.concatenate(rows)
+    assert rel(step, want) < tol
+    if precision == "f32":
+        assert rel(step, got) < 1e-5
+    m.close()
+
+
+@pytest.mark.gpu
+def test_plain_bf16_precision_is_close():
+    cfg = config([layer(ATT, DENSE), layer(SSM, DENSE), layer(ATT_PLAIN)])
+    m, o = make(cfg, 7, precision="bf16")
+    ids = tokens(90, cfg["vocab"], 8)
+    got = m.step_batch([(0, ids, all_rows(90))])
+    assert rel(got, o.forward(ids, o.new_state()).numpy()) < 5e-2
+    m.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cuts", [[2, 2, 2, 61, 3, 64, 1, 1, 30, 2], [63, 1, 1, 63, 2, 36], [1] * 5 + [95, 66], [31, 33, 32, 64, 6]])
+def test_portions_of_any_size_match_the_whole_prompt(cuts):
+    m, o = make(FULL, 9, precision="f32")
+    n = sum(cuts)
+    ids = tokens(n, FULL["vocab"], 10)
+    want = o.forward(ids, o.new_state()).numpy()
+    at, rows = 0, []
+    for c in cuts:
+        rows.append(m.step_batch([(0, ids[at:at + c], all_rows(c))]))
+        at += c
+    assert rel(np.concatenate(rows), want) < F32_TOL
+    m.close()
+
+
+@pytest.mark.gpu
+def test_unequal_requests_in_one_batch_match_each_alone():
+    m, o = make(FULL, 11, precision="f32", max_tokens=1024)
+    lens = [97, 5, 130, 64]
+    prompts = [tokens(n, FULL["vocab"], 20 + i) for i, n in enumerate(lens)]
+    want = [o.forward(p, o.new_state()).numpy() for p in prompts]
+    seqs = [0] + [m.seq_create() for _ in range(3)]
+    got = [[] for _ in lens]
+    at = [0] * 4
+    # a different mixture every step: portions of some beside single tokens of others, one request sitting a step out
+    plan = [[(0, 40), (1, 2), (2, 1)], [(2, 64), (3, 63), (0, 1)], [(1, 1), (3, 1), (0, 56), (2, 2)], [(1, 2), (2, 63)]]
+    for stepn in plan:
+        entries = [(seqs[i], prompts[i][at[i]:at[i] + c], all_rows(c)) for i, c in stepn]
+        lg = m.step_batch(entries)
+        r = 0
+        for i, c in stepn:
+            got[i].append(lg[r:r + c]); r += c; at[i] += c
+    for i in range(4):
+        g = np.concatenate(got[i])
+        assert rel(g, want[i][:len(g)]) < F32_TOL, i
+    m.close()
+
+
+@pytest.mark.gpu
+def test_pages_and_slots_are_used_again():
+    m, o = make(FULL, 13, precision="f32", max_tokens=256, max_batch=2)        # 4 pages, 2 slots
+    a, b, c = (tokens(n, FULL["vocab"], 30 + i) for i, n in enumerate((130, 120, 100)))
+    s1 = m.seq_create()
+    m.step_batch([(0, a, []), (s1, b[:60], [])])                # 3 + 1 pages: the pool is full
+    with pytest.raises(Exception):
+        m.step_batch([(s1, b[60:], [])])                        # needs a fifth page: refused, nothing changes
+    assert m.seq_len(s1) == 60
+    m.clear_kv_cache()                                          # sequence 0 gives its three pages back
+    got_b = m.step_batch([(s1, b[60:], [len(b) - 61])])
+    assert rel(got_b[0], o.forward(b, o.new_state()).numpy()[-1]) < F32_TOL
+    m.seq_free(s1)
+    s2 = m.seq_create()                                         # same slot, dirty pages and state from b
+    assert s2 == s1
+    got_c = m.step_batch([(s2, c[:50], []), (0, a[:64], [63])])
+    got_c2 = m.step_batch([(s2, c[50:], [49])])
+    assert rel(got_c2[0], o.forward(c, o.new_state()).numpy()[-1]) < F32_TOL
+    assert rel(got_c[0], o.forward(a[:64], o.new_state()).numpy()[-1]) < F32_TOL
+    m.close()
+
+
+def sharp_attention_model(seed, **opts):
+    """Scores with a spread of several units: every query looks at one or two keys anywhere in the context, and the sink is a
+    real competitor, so a lost key, a shifted edge or a missing sink moves the logits by O(1)."""
+    att = layer(ATT, None, scale=1.6, q_temp={"coef": 0.7, "every": 8})
+    cfg = config([att, layer(ATT, DENSE, kv_from=0, scale=1.2)], width=128, vocab=200)
+    import crane_b200
+    w = random_weights(cfg, seed)
+    w["l0.mix.sink"] = np.asarray([6.0, -2.0, 4.0, 0.5, 8.0, 2.0, -5.0, 3.0], np.float32)
+    w["l1.mix.sink"] = w["l0.mix.sink"][::-1].copy()
+    m = crane_b200.FosovikModel(cfg, device=0, max_tokens=1024, max_batch=2, **opts)
+    m.load_checkpoint(w.items())
+    return cfg, w, m, FosovikOracle(cfg, w)
+
+
+@pytest.mark.gpu
+def test_far_keys_page_borders_and_the_sink_with_sharp_scores():
+    cfg, w, m, o = sharp_attention_model(41, precision="f32")
+    ids = tokens(330, cfg["vocab"], 42)
+    want = o.forward(ids, o.new_state()).numpy()
+    # the oracle itself must see the effects this test is about
+    no_sink = dict(w); no_sink["l0.mix.sink"] = np.full(8, -60.0, np.float32)
+    assert rel(FosovikOracle(cfg, no_sink).forward(ids[:40], o.new_state()).numpy(), want[:40]) > 1e-2
+    st = o.new_state(); o.forward(ids[:200], st)
+    st.k[0][5] = 0; st.v[0][5] = 0                                # lose one far key
+    assert rel(o.forward(ids[200:], st).numpy(), want[200:]) > 1e-3
+    got = m.step_batch([(0, ids, all_rows(330))])
+    assert rel(got, want) < F32_TOL
+    # decode over the borders of 32-key tiles and 64-token pages, after a prompt that ends just before / on / after them
+    for start in (31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 257):
+        m.clear_kv_cache()
+        m.step_batch([(0, ids[:start], [])])
+        rows = np.concatenate([m.step_batch([(0, [t], [0])]) for t in ids[start:start + 4]])
+        assert rel(rows, want[start:start + 4]) < F32_TOL, start
+    m.close()
+
+
+@pytest.mark.gpu
+def test_first_tokens_of_a_sequence():
+    m, o = make(FULL, 15, precision="f32")
+    ids = tokens(6, FULL["vocab"], 16)
+    want = o.forward(ids, o.new_state()).numpy()
+    assert rel(m.step_batch([(0, ids[:1], [0])]), want[:1]) < F32_TOL           # a one-token prompt: empty conv window, one key
+    assert rel(m.step_batch([(0, ids[1:2], [0])]), want[1:2]) < F32_TOL
+    assert rel(m.step_batch([(0, ids[2:], [0, 1, 2, 3])]), want[2:]) < F32_TOL
+    m.close()
+
+
+@pytest.mark.gpu
+def test_long_context_decode_uses_split_keys():
+    cfg = config([layer(ATT, DENSE, scale=1.4), layer(SSM)], width=128, vocab=150)
+    m, o = make(cfg, 17, precision="f32", max_tokens=2048)
+    ids = tokens(1500, cfg["vocab"], 18)
+    want = o.forward(ids, o.new_state()).numpy()
+    m.step_batch([(0, ids[:1490], [])])
+    rows = np.concatenate([m.step_batch([(0, [t], [0])]) for t in ids[1490:]])
+    assert rel(rows, want[1490:]) < F32_TOL
+    m.close()
+
+
+@pytest.mark.gpu
+def test_greedy_generation_through_generate_and_the_scheduler():
+    from crane_b200.scheduler import BatchScheduler
+    m, o = make(FULL, 19, precision="f32", max_tokens=512)
+
+    def oracle_greedy(prompt, n):
+        st = o.new_state()
+        lg = o.forward(prompt, st).numpy()[-1]
+        out, margins = [], []
+        for _ in range(n):
+            top = np.sort(lg)[-2:]
+            margins.append(top[1] - top[0])
+            out.append(int(lg.argmax()))
+            lg = o.forward([out[-1]], st).numpy()[-1]
+        return out, min(margins)
+
+    prompts = [tokens(n, FULL["vocab"], 50 + i) for i, n in enumerate((70, 9, 33, 130, 20, 64))]
+    want = [oracle_greedy(p, 12) for p in prompts]
+    assert min(mg for _, mg in want) > 1e-4                     # no decision of this test is a close call
+    assert m.generate(prompts[0], max_new_tokens=12).tolist() == want[0][0]
+    m.clear_kv_cache()
+    sch = BatchScheduler(m, chunk=48, max_live=3, token_budget=80)
+    rids = [sch.add(p, 12) for p in prompts]
+    out = sch.run()
+    for rid, (toks, _) in zip(rids, want):
+        assert out[rid] == toks, rid
+    # sampling through the same path: temperature with top-k 1 is greedy whatever the draw
+    sch = BatchScheduler(m, chunk=32, max_live=2)
+    rid = sch.add(prompts[1], 6, temperature=0.8, top_k=1, seed=3)
+    assert sch.run()[rid] == want[1][0][:6]
+    # batched decode entry point: two sequences side by side
+    m.clear_kv_cache()
+    s1 = m.seq_create()
+    m.step_batch([(0, prompts[2], []), (s1, prompts[4], [])][:2])
+    first = [want[2][0][0], want[4][0][0]]
+    toks, _ = m.decode_batch([0, s1], first, n_steps=5)
+    assert toks[0].tolist() == want[2][0][1:6] and toks[1].tolist() == want[4][0][1:6]
+    m.close()
+
+
+@pytest.mark.gpu
+def test_model_folder_loader_and_trace_runner(tmp_path):
+    import json, os, struct, subprocess, sys
+    cfg = SINGLE["shared_kv"]
+    w = random_weights(cfg, 23)
+    hdr, blob = {}, b""
+    for k, a in w.items():
+        bits = (np.ascontiguousarray(a, np.float32).view(np.uint32) >> 16).astype(np.uint16).tobytes()
+        hdr[k] = {"dtype": "BF16", "shape": list(np.shape(a)), "data_offsets": [len(blob), len(blob) + len(bits)]}
+        blob += bits
+    mdir = tmp_path / "model"; mdir.mkdir()
+    (mdir / "config.json").write_text(json.dumps(cfg))
+    h = json.dumps(hdr).encode()
+    (mdir / "model.safetensors").write_bytes(struct.pack("<Q", len(h)) + h + blob)
+    o = FosovikOracle(cfg, w)
+    a, b = tokens(75, cfg["vocab"], 24), tokens(20, cfg["vocab"], 25)
+    wa, wb = o.forward(a, o.new_state()).numpy(), o.forward(b, o.new_state()).numpy()
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:70], "want": [0, 69]}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": b[:2], "want": []}, {"id": "a", "tokens": a[70:71], "want": [0]}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[71:], "want": [3]}, {"id": "b", "tokens": b[2:], "want": [17]}], "end": ["a", "b"]},
+             {"step": 3, "entries": [{"id": "c", "tokens": b, "want": [19]}], "end": ["c"]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for dtype, tol in (("float32", F32_TOL), ("bfloat16", SPLIT_TOL)):
+        out = tmp_path / dtype
+        r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(mdir), "--dtype", dtype, "--out", str(out),
+                            "--max-tokens", "192"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done %d" % i for i in range(4)]
+        V = cfg["vocab"]
+        rd = lambda i: np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)
+        assert rel(rd(0), wa[[0, 69]]) < tol and rel(rd(1), wa[[70]]) < tol
+        assert rel(rd(2), np.stack([wa[74], wb[19]])) < tol and rel(rd(3), wb[[19]]) < tol

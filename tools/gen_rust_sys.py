@@ -13,7 +13,8 @@ OUT = os.path.join(ROOT, "rust", "crane-b200-sys", "src", "lib.rs")
 
 BASE = {"int": "c_int", "void": "c_void", "char": "c_char", "float": "f32", "double": "f64", "size_t": "usize", "uint8_t": "u8",
         "uint16_t": "u16", "uint32_t": "u32", "uint64_t": "u64", "int32_t": "i32", "int64_t": "i64", "unsigned char": "u8",
-        "crane_b200_model": "crane_b200_model", "crane_b200_logits": "crane_b200_logits", "crane_b200_sampling": "crane_b200_sampling"}
+        "crane_b200_model": "crane_b200_model", "crane_b200_logits": "crane_b200_logits", "crane_b200_sampling": "crane_b200_sampling",
+        "crane_b200_step_entry": "crane_b200_step_entry"}
 
 
 def rust_type(c: str) -> str:
@@ -71,7 +72,7 @@ def generate() -> str:
                 k, v = [x.strip() for x in item.split("=")]
                 out.append(f"pub const {k}: c_int = {v};")
         out.append("")
-    for st in ("crane_b200_logits", "crane_b200_sampling"):
+    for st in ("crane_b200_logits", "crane_b200_sampling", "crane_b200_step_entry"):
         out += ["#[repr(C)]", "#[derive(Clone, Copy)]", f"pub struct {st} {{"]
         out += [f"    pub {n}: {t}," for n, t in parse_struct(text, st)]
         out += ["}", ""]
