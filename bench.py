@@ -388,6 +388,83 @@ def bench_config2(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def bench_fosovik(args, rank, world, local_rank):
+    """The Fosovik layer-list decoder at the Qwen3.5-0.8B hybrid's size (width 1024, 18 Mamba-2 + 6 sink-attention layers with
+    256-wide heads, vocabulary 248 320), once with the dense clamped feed-forward (3 584 wide) and once with a mixture of 8 experts
+    (896 wide, 4 per token: the same active width); one request = 4096-token prefill + 512 greedy decode tokens through
+    `crane_b200_generate_greedy`, as `--config qwen3_5_0_8b` measures the closest existing model, whose line (a child process on the
+    same GPU) is attached as `closest_model`.  Random bf16 blocks as weights (timing only); one GPU."""
+    import crane_b200
+    sys.path.insert(0, os.path.join(ROOT, "tools"))
+    import bench_configs as bc
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has no model of this design"}))
+        return
+    if rank != 0:
+        return
+    S, n_dec = 4096, 512
+    peaks = load_peaks()
+    sampler = ClockSampler(0)
+    variants = {}
+    for name, moe in (("dense_ff3584", None), ("moe_8x896_top4", (8, 4, 896))):
+        cfg = synth.fosovik_config(moe=moe)
+        m = crane_b200.FosovikModel(cfg, device=0, max_tokens=S + n_dec + 128, max_batch=4)
+        bc.load_cheap(m, cfg)
+        ids = synth.synth_token_ids(S, cfg["vocab"], "fsv-" + name)
+
+        def request():
+            m.clear_kv_cache()
+            t0 = time.perf_counter()
+            out = m.generate_greedy(ids, n_dec + 1)
+            wall = time.perf_counter() - t0
+            t = m.last_timing()
+            return wall, t["prefill_ms"], t["decode_ms"], len(out) - 1
+        for _ in range(max(args.warmup, 3)):
+            request()
+        if name == "dense_ff3584":
+            sampler.start()
+        l0 = m.kernel_launches()
+        rs = [request() for _ in range(args.steps)]
+        launches = m.kernel_launches() - l0
+        W, V = cfg["width"], cfg["vocab"]
+        wts = sum(int(np.prod(sh)) for n, sh, k in synth.tensor_specs(cfg) if len(sh) == 2 and n != "embed")
+        if moe:          # a token reads `top` of `experts` expert matrices
+            ex = sum(int(np.prod(sh)) for n, sh, k in synth.tensor_specs(cfg) if ".mlp.e" in n)
+            wts -= ex * (moe[0] - moe[1]) // moe[0]
+        att = [L["mixer"] for L in cfg["layers"] if L["type"] == "attention"]
+        ssm = [L["mixer"] for L in cfg["layers"] if L["type"] == "mamba2"]
+        ctx = S + n_dec / 2
+        kv_b = sum(2 * a["kv_heads"] * a["dim"] * 4 for a in att)                               # hi + lo bf16 planes
+        st_b = sum(2 * 4 * s_["heads"] * s_["state"] * s_["vdim"] for s_ in ssm)                # state read and written
+        by = 2 * wts + ctx * kv_b + st_b
+        fl = 2 * (wts - V * W) * S + sum(4 * S * (S / 2) * a["heads"] * a["dim"] for a in att) + 2 * V * W
+        dec_s = sum(r[2] for r in rs) / 1e3
+        ntok = sum(r[3] for r in rs)
+        pre_s = sum(r[1] for r in rs) / 1e3
+        variants[name] = {"decode_tok_s": ntok / dec_s, "decode_us_per_step": 1e6 * dec_s / ntok, "prefill_ms": 1e3 * pre_s / len(rs),
+                          "prefill_tflops": fl * len(rs) / pre_s / 1e12, "prefill_frac_of_bf16_peak": fl * len(rs) / pre_s / 1e12 / peaks["bf16_tflops"],
+                          "decode_hbm_gbs": by / (dec_s / ntok) / 1e9, "decode_roofline_frac": by / (dec_s / ntok) / 1e9 / peaks["hbm_gbs"],
+                          "algorithmic_bytes_per_step": by, "prefill_flop": fl, "e2e_tok_s": ntok / sum(r[0] for r in rs), "gpu_launches": int(launches)}
+        m.close()
+    clocks = sampler.summary()
+    d = variants["dense_ff3584"]
+    out = {"metric": "decode_tok_per_s", "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": f"Fosovik layer-list decoder at Qwen3.5-0.8B's size (18 Mamba-2 + 6 sink-attention layers, width 1024), {S}-token prefill + {n_dec} greedy decode tokens per request",
+                      "weights": "random bf16 blocks (timing only)", "l2": "per-token weight stream 1.4 GB >> 126 MB L2", "parallelism": "1 GPU",
+                      "precision": os.environ.get("CRANE_B200_PRECISION", "split")},
+           "value": d["decode_tok_s"], "ms_per_step": 1e3 / d["e2e_tok_s"] * n_dec, "prefill_ms": d["prefill_ms"], "prefill_tflops": d["prefill_tflops"],
+           "e2e": {"value": d["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": int(S * 4), "d2h_bytes_per_step": int((n_dec + 1) * 4),
+                   "api": "crane_b200_generate_greedy (host prompt ids in, host token ids out; prefill inside the timed region)"},
+           "gpu_launches": d["gpu_launches"], "clocks": clocks, "variants": variants,
+           "roofline": {"bound": "hbm", "achieved": d["decode_hbm_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": d["decode_roofline_frac"],
+                        "peak_source": peaks["source"], "launch": "one decode step (graph replay): weights once + recurrent states + KV of 6 layers"}}
+    if not args.no_other_configs:
+        out["closest_model"] = other_config_summary("qwen3_5_0_8b", steps=args.steps)
+    print(json.dumps(out))
+
+
 def other_config_summary(config, steps=2, timeout_s=120):
     """One more BASELINE config measured by THIS script in a child process (`bench.py --config <config>`), condensed for the headline
     line's `other_configs` field.  A child, so that nothing it does -- a failure, a hang (killed at the timeout) -- can keep the
@@ -416,7 +493,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="crane_b200", choices=["crane_b200", "reference"])
-    ap.add_argument("--config", default="qwen3_vl_2b", choices=["qwen3_vl_2b", "tiny", "qwen3_8b_q4km", "qwen3_5_0_8b"])
+    ap.add_argument("--config", default="qwen3_vl_2b", choices=["qwen3_vl_2b", "tiny", "qwen3_8b_q4km", "qwen3_5_0_8b", "fosovik"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the config-2 (Qwen3.5-0.8B) child measurement appended to the headline line")
     args = ap.parse_args()
@@ -428,6 +505,8 @@ def main():
         return bench_config4(args, rank, world, local_rank)
     if args.config == "qwen3_5_0_8b":
         return bench_config2(args, rank, world, local_rank)
+    if args.config == "fosovik":
+        return bench_fosovik(args, rank, world, local_rank)
     cfg = synth.QWEN3_VL_2B if args.config == "qwen3_vl_2b" else synth.TINY_QWEN3_VL
     name = "Qwen3-VL-2B" if args.config == "qwen3_vl_2b" else "tiny-Qwen3-VL"
     workload = f"{name} bf16, 1x(448x448) image + {N_TEXT}-tok prompt, prefill + {N_DECODE} greedy decode tokens per request"

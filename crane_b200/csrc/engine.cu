@@ -1958,7 +1958,10 @@ int crane_b200_forward_step(crane_b200_model* m, const uint32_t* ids, size_t n, 
     if (m->fsv) {              // one entry: the current sequence, logits of its last row
         const uint32_t last = (uint32_t)(n - 1);
         const crane_b200_step_entry e{m->cur, ids, n, &last, 1};
+        CUDA_OK(cudaEventRecord(n > 1 ? m->pev0 : m->dev0, m->stream));
         m->fsv_step(&e, 1);
+        CUDA_OK(cudaEventRecord(n > 1 ? m->pev1 : m->dev1, m->stream));
+        if (n == 1) m->last_decode_steps = 1;
     } else if (n == 1) {
         CUDA_OK(cudaEventRecord(m->dev0, m->stream));
         m->arm_state(ids[0], start_pos, (int)start_pos, (int)start_pos, (int)start_pos);
@@ -2095,22 +2098,21 @@ int crane_b200_decode_greedy(crane_b200_model* m, uint32_t first_token, size_t s
     if (n_steps > (size_t)m->out_cap) fail(CRANE_B200_INVALID_ARG, "decode_greedy: n_steps %zu > %d", n_steps, m->out_cap);
     if (first_token >= (uint32_t)m->V) fail(CRANE_B200_INVALID_ARG, "token id %u >= vocab %d", first_token, m->V);
     check_room(m, start_pos, n_steps);
-    if (m->fsv) {             // one ragged step per token; the argmax stays on the device until the 4-byte read
-        uint32_t tok = first_token;
-        const uint32_t zero = 0;
-        size_t cnt = 0;
+    if (m->fsv) {             // n_steps graph replays on the device; the tokens come back in one read
+        std::vector<uint32_t> toks(n_steps);
         CUDA_OK(cudaEventRecord(m->dev0, m->stream));
+        m->fsv->greedy_loop(&m->cur, &first_token, 1, (int)n_steps, toks.data());
+        CUDA_OK(cudaEventRecord(m->dev1, m->stream));
+        m->logits = m->fsv->logits; m->launches = m->fsv->launches;
+        m->kv_len = (size_t)m->fsv->seqs[m->cur].len; m->seq_kv[m->cur] = m->kv_len;
+        m->last_decode_steps = n_steps;
+        size_t cnt = 0;
         for (size_t i = 0; i < n_steps; ++i) {
-            const crane_b200_step_entry e{m->cur, &tok, 1, &zero, 1};
-            m->fsv_step(&e, 1);
-            m->fsv_greedy_rows(1, &tok);
-            tokens_out[cnt++] = tok;
+            tokens_out[cnt++] = toks[i];
             bool stop = false;
-            for (size_t k = 0; k < n_eos; ++k) stop = stop || (eos_ids && tok == eos_ids[k]);
+            for (size_t k = 0; k < n_eos; ++k) stop = stop || (eos_ids && toks[i] == eos_ids[k]);
             if (stop) break;
         }
-        CUDA_OK(cudaEventRecord(m->dev1, m->stream));
-        m->last_decode_steps = cnt;
         *n_out = cnt;
         return CRANE_B200_OK;
     }
@@ -2422,18 +2424,19 @@ int crane_b200_decode_batch(crane_b200_model* m, const int* seqs, const uint32_t
     need_ready(m);
     if (!seqs || !tokens || !tokens_out || n == 0 || n_steps == 0) fail(CRANE_B200_INVALID_ARG, "decode_batch: bad arguments");
     if (m->hybrid) fail(CRANE_B200_UNSUPPORTED, "decode_batch on the hybrid model");
-    if (m->fsv) {             // every round is one ragged step of n single-token entries
-        std::vector<uint32_t> cur_tok(tokens, tokens + n), next(n);
-        std::vector<crane_b200_step_entry> es(n);
-        const uint32_t zero = 0;
-        for (size_t t = 0; t < n_steps; ++t) {
-            for (size_t i = 0; i < n; ++i) es[i] = crane_b200_step_entry{seqs[i], &cur_tok[i], 1, &zero, 1};
-            m->fsv_step(es.data(), n);
-            if (logits_host && t + 1 == n_steps)
-                CUDA_OK(cudaMemcpyAsync(logits_host, m->logits, n * (size_t)m->V * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
-            m->fsv_greedy_rows(n, next.data());
-            for (size_t i = 0; i < n; ++i) { tokens_out[i * n_steps + t] = next[i]; cur_tok[i] = next[i]; }
+    if (m->fsv) {             // every round is one ragged step of n single-token entries, replayed on the device
+        std::vector<int> sq(seqs, seqs + n);
+        for (size_t i = 0; i < n; ++i) if (tokens[i] >= (uint32_t)m->V) fail(CRANE_B200_INVALID_ARG, "token id %u >= vocab %d", tokens[i], m->V);
+        CUDA_OK(cudaEventRecord(m->dev0, m->stream));
+        m->fsv->greedy_loop(sq.data(), tokens, (int)n, (int)n_steps, tokens_out);
+        CUDA_OK(cudaEventRecord(m->dev1, m->stream));
+        m->logits = m->fsv->logits; m->launches = m->fsv->launches;
+        if (logits_host) {
+            CUDA_OK(cudaMemcpyAsync(logits_host, m->logits, n * (size_t)m->V * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
+            CUDA_OK(cudaStreamSynchronize(m->stream));
         }
+        for (int i = 0; i < m->max_batch; ++i) m->seq_kv[i] = (size_t)m->fsv->seqs[i].len;
+        m->kv_len = m->seq_kv[m->cur];
         m->last_decode_steps = n_steps;
         return CRANE_B200_OK;
     }

@@ -255,8 +255,9 @@ flash_prefill_kernel(FlashArgs a) {
     const int S = a.seq_len ? a.seq_len[z] : a.S;
     const int q0 = blockIdx.x * BM;
     if (q0 >= S) return;
-    const int kv_off = CAUSAL ? a.kv_offset : 0;
+    const int kv_off = CAUSAL ? (a.seq_kv_offset ? a.seq_kv_offset[z] : a.kv_offset) : 0;
     const int T = CAUSAL ? (kv_off + S) : S;   // keys available
+    const int* btab = (PAGED && a.seq_slot) ? a.block_table + (size_t)a.seq_slot[z] * a.bt_stride : a.block_table;
     const int kvh = head / (a.nh / a.nkv);
     const int n_tiles = CAUSAL ? min((T + BN - 1) / BN, (kv_off + q0 + BM - 1) / BN + 1) : (T + BN - 1) / BN;
 
@@ -278,7 +279,7 @@ flash_prefill_kernel(FlashArgs a) {
             const bool ok = t < T;
             const bf16 *ksrc, *vsrc;
             if (PAGED) {
-                const int page = a.block_table[kv0 / KV_PAGE];     // a tile is a whole page or an aligned half of one
+                const int page = btab[kv0 / KV_PAGE];     // a tile is a whole page or an aligned half of one
                 const size_t off = (((size_t)page * a.nkv + kvh) * KV_PAGE + (kv0 % KV_PAGE) + r) * D + ch * 8;
                 ksrc = a.k_pool + off; vsrc = a.v_pool + off;
             } else {
@@ -467,6 +468,7 @@ flash_prefill_kernel(FlashArgs a) {
             const float mo = d[D / 2 + r], lo = d[D / 2 + 2 + r];
             const float mn = fmaxf(m_row[r], mo);
             const float c0 = (m_row[r] == -INFINITY) ? 0.f : exp2f(m_row[r] - mn), c1 = (mo == -INFINITY) ? 0.f : exp2f(mo - mn);
+            m_row[r] = mn;
             l_row[r] = l_row[r] * c0 + lo * c1;
 #pragma unroll
             for (int i = 0; i < D / 8; ++i) {
@@ -485,7 +487,12 @@ flash_prefill_kernel(FlashArgs a) {
     for (int r = 0; r < 2; ++r) {
         const int qrow = q0 + warp * 16 + g + r * 8;
         if (qrow < S) {
-            const float inv = 1.f / l_row[r];
+            float inv = 1.f / l_row[r];
+            if (a.sink) {        // the sink joins the denominator only: rescale to the larger of the row maximum and the sink
+                const float s2 = a.sink[head] * 1.4426950408889634f, mn = fmaxf(m_row[r], s2);
+                const float c = exp2f(m_row[r] - mn);
+                inv = c / (l_row[r] * c + exp2f(s2 - mn));
+            }
             bf16* o = a.out + (size_t)(row0 + qrow) * a.o_stride + head * D;
 #pragma unroll
             for (int i = 0; i < D / 8; ++i) {

@@ -51,6 +51,12 @@ struct FlashArgs {
     int max_len;                        // max query rows over sequences (grid sizing)
     // split precision (x = hi + lo, both bf16): element offsets of the low-order planes, 0 = plain bf16
     long long q_lo_off, kv_lo_off, out_lo_off;
+    // ragged batches over paged caches (seq_start / seq_len set): sequence z reads block_table + seq_slot[z] * bt_stride and sees
+    // seq_kv_offset[z] cached keys before its first row (nullptr: the single table and kv_offset above)
+    const int* seq_kv_offset = nullptr;
+    const int* seq_slot = nullptr;
+    int bt_stride = 0;
+    const float* sink = nullptr;        // [nh]: one extra term exp(sink_h) in every row's softmax denominator (no key, no value, unscaled)
 };
 
 // quantised KV pages <-> the bf16 (hi + lo) scratch the prefill kernels read and write (see prefill.cu)

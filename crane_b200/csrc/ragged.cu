@@ -7,6 +7,8 @@
 #include "ragged.cuh"
 #include "decode.cuh"
 
+#include <algorithm>
+
 namespace cb {
 
 namespace {
@@ -21,12 +23,20 @@ __device__ __forceinline__ void store_act(const ActOut& o, int r, int c, float v
     }
 }
 
-template <typename KT> __device__ __forceinline__ float kv_load(const KT* p);
-template <> __device__ __forceinline__ float kv_load<float>(const float* p) { return *p; }
-template <> __device__ __forceinline__ float kv_load<bf16>(const bf16* p) { return __bfloat162float(*p); }
-template <typename KT> __device__ __forceinline__ void kv_store(KT* p, float v);
-template <> __device__ __forceinline__ void kv_store<float>(float* p, float v) { *p = v; }
-template <> __device__ __forceinline__ void kv_store<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+// KV page elements: f32, or bf16 with an optional low-order plane `lo` elements further on (x ~= hi + lo, ~16 mantissa bits)
+template <typename KT> __device__ __forceinline__ float kv_load(const KT* p, long long lo);
+template <> __device__ __forceinline__ float kv_load<float>(const float* p, long long) { return *p; }
+template <> __device__ __forceinline__ float kv_load<bf16>(const bf16* p, long long lo) {
+    const float h = __bfloat162float(*p);
+    return lo ? h + __bfloat162float(p[lo]) : h;
+}
+template <typename KT> __device__ __forceinline__ void kv_store(KT* p, float v, long long lo);
+template <> __device__ __forceinline__ void kv_store<float>(float* p, float v, long long) { *p = v; }
+template <> __device__ __forceinline__ void kv_store<bf16>(bf16* p, float v, long long lo) {
+    const bf16 h = __float2bfloat16_rn(v);
+    *p = h;
+    if (lo) p[lo] = __float2bfloat16_rn(v - __bfloat162float(h));
+}
 
 // ---------------------------------------------------------------------------------------------------------------- rows
 __global__ void embed_scale_rows_kernel(const int* __restrict__ ids, int T, const bf16* __restrict__ embed, int W, float scale,
@@ -107,18 +117,17 @@ __global__ void attn_prep_kernel(RaggedBatch rb, AttnPrepArgs a) {
             ss = warp_sum(ss);
             const float inv = 1.f / sqrtf(ss / (float)a.d + a.eps) * (isq ? temp : 1.f);
             if (isq) {
-                float* dst = a.q_out + (size_t)r * a.ldq + (size_t)hh * a.d;
-                for (int c = lane; c < a.d; c += 32) dst[c] = src[c] * inv;
+                for (int c = lane; c < a.d; c += 32) store_act(a.q_out, r, hh * a.d + c, src[c] * inv);
             } else {
                 const int g = hh - a.H;
                 KT* dst = (KT*)a.k_pool + (((size_t)page * a.G + g) * KV_PAGE + (pos % KV_PAGE)) * a.d;
-                for (int c = lane; c < a.d; c += 32) kv_store<KT>(dst + c, src[c] * inv);
+                for (int c = lane; c < a.d; c += 32) kv_store<KT>(dst + c, src[c] * inv, a.kv_lo_off);
             }
         } else {
             const int g = hh - a.H - a.G;
             const float* src = row + (size_t)(a.H + a.G) * a.d + (size_t)g * a.dv;
             KT* dst = (KT*)a.v_pool + (((size_t)page * a.G + g) * KV_PAGE + (pos % KV_PAGE)) * a.dv;
-            for (int c = lane; c < a.dv; c += 32) kv_store<KT>(dst + c, src[c]);
+            for (int c = lane; c < a.dv; c += 32) kv_store<KT>(dst + c, src[c], a.kv_lo_off);
         }
     }
 }
@@ -145,7 +154,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
     float m = -INFINITY, l = 0.f, acc[ATT_MAXC];
 #pragma unroll
     for (int c = 0; c < ATT_MAXC; ++c) acc[c] = 0.f;
-    const bool vec = (d & 3) == 0 && sizeof(KT) == 4;
+    const bool vec = sizeof(KT) == 4 ? (d & 3) == 0 : (d & 7) == 0;
+    const bool vvec = (dv & 7) == 0;        // value columns 8 * lane .. 8 * lane + 7 per lane (16-byte loads) instead of lane + 32 c
     for (int t = t_lo + warp; t < t_hi; t += ATT_WARPS) {
         const int j = t * 32 + lane;
         const int pg = bt[(t * 32) / KV_PAGE];           // a 32-key tile never straddles a 64-token page
@@ -154,15 +164,31 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
         if (j < nkeys) {
             const KT* kr = (const KT*)a.k_pool + (base + lane) * d;
             float dot = 0.f;
-            if (vec) {
+            if (vec && sizeof(KT) == 4) {
                 const float4* k4 = reinterpret_cast<const float4*>(kr);
                 for (int c = 0; c < d / 4; ++c) {
                     const float4 kk = k4[c];
                     dot = fmaf(sq[4 * c], kk.x, dot); dot = fmaf(sq[4 * c + 1], kk.y, dot);
                     dot = fmaf(sq[4 * c + 2], kk.z, dot); dot = fmaf(sq[4 * c + 3], kk.w, dot);
                 }
+            } else if (vec) {                            // 8 bf16 per 16-byte load, the low-order plane added as it comes
+                const uint4* k8 = reinterpret_cast<const uint4*>(kr);
+                const uint4* l8 = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(kr) + a.kv_lo_off);
+                for (int c = 0; c < d / 8; ++c) {
+                    const uint4 kk = k8[c];
+                    float k0 = bf16lo(kk.x), k1 = bf16hi(kk.x), k2 = bf16lo(kk.y), k3 = bf16hi(kk.y);
+                    float k4 = bf16lo(kk.z), k5 = bf16hi(kk.z), k6 = bf16lo(kk.w), k7 = bf16hi(kk.w);
+                    if (a.kv_lo_off) {
+                        const uint4 ll = l8[c];
+                        k0 += bf16lo(ll.x); k1 += bf16hi(ll.x); k2 += bf16lo(ll.y); k3 += bf16hi(ll.y);
+                        k4 += bf16lo(ll.z); k5 += bf16hi(ll.z); k6 += bf16lo(ll.w); k7 += bf16hi(ll.w);
+                    }
+                    const float* qq = sq + 8 * c;
+                    dot = fmaf(qq[0], k0, dot); dot = fmaf(qq[1], k1, dot); dot = fmaf(qq[2], k2, dot); dot = fmaf(qq[3], k3, dot);
+                    dot = fmaf(qq[4], k4, dot); dot = fmaf(qq[5], k5, dot); dot = fmaf(qq[6], k6, dot); dot = fmaf(qq[7], k7, dot);
+                }
             } else {
-                for (int c = 0; c < d; ++c) dot = fmaf(sq[c], kv_load<KT>(kr + c), dot);
+                for (int c = 0; c < d; ++c) dot = fmaf(sq[c], kv_load<KT>(kr + c, a.kv_lo_off), dot);
             }
             s = dot;
         }
@@ -176,12 +202,38 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
         m = mn;
         const int cnt = min(32, nkeys - t * 32);
         const KT* vb = (const KT*)a.v_pool + base * dv;
-        for (int jj = 0; jj < cnt; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, p, jj);
+        if (vvec) {
+            const bool mine = 8 * lane < dv;
+            for (int jj = 0; jj < cnt; ++jj) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);
+                if (!mine) continue;
+                float v[8];
+                if (sizeof(KT) == 4) {
+                    const float4* v4 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(vb) + (size_t)jj * dv + 8 * lane);
+                    const float4 x0 = v4[0], x1 = v4[1];
+                    v[0] = x0.x; v[1] = x0.y; v[2] = x0.z; v[3] = x0.w; v[4] = x1.x; v[5] = x1.y; v[6] = x1.z; v[7] = x1.w;
+                } else {
+                    const bf16* vp = reinterpret_cast<const bf16*>(vb) + (size_t)jj * dv + 8 * lane;
+                    const uint4 hh = *reinterpret_cast<const uint4*>(vp);
+                    v[0] = bf16lo(hh.x); v[1] = bf16hi(hh.x); v[2] = bf16lo(hh.y); v[3] = bf16hi(hh.y);
+                    v[4] = bf16lo(hh.z); v[5] = bf16hi(hh.z); v[6] = bf16lo(hh.w); v[7] = bf16hi(hh.w);
+                    if (a.kv_lo_off) {
+                        const uint4 ll = *reinterpret_cast<const uint4*>(vp + a.kv_lo_off);
+                        v[0] += bf16lo(ll.x); v[1] += bf16hi(ll.x); v[2] += bf16lo(ll.y); v[3] += bf16hi(ll.y);
+                        v[4] += bf16lo(ll.z); v[5] += bf16hi(ll.z); v[6] += bf16lo(ll.w); v[7] += bf16hi(ll.w);
+                    }
+                }
 #pragma unroll
-            for (int c = 0; c < ATT_MAXC; ++c) {
-                const int col = lane + 32 * c;
-                if (col < dv) acc[c] = fmaf(pj, kv_load<KT>(vb + (size_t)jj * dv + col), acc[c]);
+                for (int c = 0; c < 8; ++c) acc[c] = fmaf(pj, v[c], acc[c]);
+            }
+        } else {
+            for (int jj = 0; jj < cnt; ++jj) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);
+#pragma unroll
+                for (int c = 0; c < ATT_MAXC; ++c) {
+                    const int col = lane + 32 * c;
+                    if (col < dv) acc[c] = fmaf(pj, kv_load<KT>(vb + (size_t)jj * dv + col, a.kv_lo_off), acc[c]);
+                }
             }
         }
     }
@@ -189,7 +241,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
     float* wm = sm; float* wl = sm + ATT_WARPS; float* wa = sm + 2 * ATT_WARPS;
     if (lane == 0) { wm[warp] = m; wl[warp] = l; }
 #pragma unroll
-    for (int c = 0; c < ATT_MAXC; ++c) { const int col = lane + 32 * c; if (col < dv) wa[warp * dv + col] = acc[c]; }
+    for (int c = 0; c < ATT_MAXC; ++c) { const int col = vvec ? 8 * lane + c : lane + 32 * c; if (col < dv) wa[warp * dv + col] = acc[c]; }
     __syncthreads();
     float M = -INFINITY;
     for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, wm[w]);
@@ -212,23 +264,28 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
 }
 
 __global__ void sink_attention_merge_kernel(SinkAttnArgs a) {
-    const int r = blockIdx.x, h = blockIdx.y, dv = a.dv;
-    const float* pp = a.part + ((size_t)r * a.H + h) * a.nsplit * (dv + 2);
+    __shared__ float wgt[64];
+    __shared__ float Ls;
+    const int r = blockIdx.x, h = blockIdx.y, dv = a.dv, ns = a.nsplit;           // nsplit <= 64
+    const float* pp = a.part + ((size_t)r * a.H + h) * ns * (dv + 2);
     const float sink = a.sink ? a.sink[h] : -INFINITY;
-    float Mx = sink;
-    for (int s = 0; s < a.nsplit; ++s) Mx = fmaxf(Mx, pp[(size_t)s * (dv + 2)]);
-    float L = (sink == -INFINITY) ? 0.f : __expf(sink - Mx);
-    for (int s = 0; s < a.nsplit; ++s) {
-        const float ms = pp[(size_t)s * (dv + 2)];
-        if (ms != -INFINITY) L += pp[(size_t)s * (dv + 2) + 1] * __expf(ms - Mx);
+    if (threadIdx.x < 32) {                 // one warp: the maximum over the splits and the sink, then each split's weight, in split order
+        const int lane = threadIdx.x;
+        const float m0 = lane < ns ? pp[(size_t)lane * (dv + 2)] : -INFINITY, m1 = lane + 32 < ns ? pp[(size_t)(lane + 32) * (dv + 2)] : -INFINITY;
+        const float Mx = fmaxf(warp_max(fmaxf(m0, m1)), sink);
+        const float w0 = m0 == -INFINITY ? 0.f : __expf(m0 - Mx), w1 = m1 == -INFINITY ? 0.f : __expf(m1 - Mx);
+        wgt[lane] = w0; wgt[lane + 32] = w1;
+        const float l0 = lane < ns ? pp[(size_t)lane * (dv + 2) + 1] * w0 : 0.f, l1 = lane + 32 < ns ? pp[(size_t)(lane + 32) * (dv + 2) + 1] * w1 : 0.f;
+        const float L = warp_sum(l0 + l1) + (sink == -INFINITY ? 0.f : __expf(sink - Mx));
+        if (lane == 0) Ls = L;
     }
+    __syncthreads();
+    const float invL = 1.f / Ls;
     for (int col = threadIdx.x; col < dv; col += blockDim.x) {
         float o = 0.f;
-        for (int s = 0; s < a.nsplit; ++s) {
-            const float ms = pp[(size_t)s * (dv + 2)];
-            if (ms != -INFINITY) o += pp[(size_t)s * (dv + 2) + 2 + col] * __expf(ms - Mx);
-        }
-        store_act(a.out, r, h * dv + col, o / L);
+#pragma unroll 4
+        for (int sp = 0; sp < ns; ++sp) o = fmaf(pp[(size_t)sp * (dv + 2) + 2 + col], wgt[sp], o);
+        store_act(a.out, r, h * dv + col, o * invL);
     }
 }
 
@@ -260,46 +317,84 @@ __global__ void conv_window_kernel(RaggedBatch rb, Mamba2Args a, int C, int col0
     }
 }
 
-// Selective scan, one block per (entry, head, 128-column slice of P); thread (p, ns) owns state rows n = ns, ns + 8, ...
-constexpr int SSD_NS = 8, SSD_MAXR = 32;      // N <= 256
-__global__ void ssd_scan_kernel(RaggedBatch rb, Mamba2Args a, int C) {
+// Selective scan.  Block = (entry, head, slice of SSD_COLS value columns); thread (p, ns) owns state rows n = ns, ns + 8, ... of
+// column p in registers for the whole portion.  The recurrence itself is one FMA deep per token; what would serialise it is the
+// operand fetch, so the step inputs (x slice, B, C, dt) of SSD_CH tokens at a time are staged in shared memory with cp.async,
+// double-buffered: chunk c + 1 is in flight while chunk c is consumed.  dt = softplus(.) and the decay exp(-exp(A) dt) are
+// computed once per token, in f32, when its chunk lands.
+constexpr int SSD_NS = 8, SSD_MAXR = 32, SSD_COLS = 32, SSD_CH = 16;      // N <= 256; 32 columns x 8 = 256 threads per block
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+template <int SSD_R>                                         // state rows per thread: ceil(N / 8) rounded up to 4, 8, 16 or 32
+__global__ void __launch_bounds__(SSD_COLS * SSD_NS) ssd_scan_kernel(RaggedBatch rb, Mamba2Args a, int C) {
+    extern __shared__ float ssm_s[];
     const int e = blockIdx.x, h = blockIdx.y, ns = threadIdx.x & (SSD_NS - 1), pl = threadIdx.x / SSD_NS;
-    const int p = blockIdx.z * (blockDim.x / SSD_NS) + pl;
+    const int p0 = blockIdx.z * SSD_COLS, p = p0 + pl;
     const int P = a.P, N = a.N, inner = a.heads * P, g = h / (a.heads / a.groups);
     const bool live = p < P;
     const int len = rb.ent_len[e], r0 = rb.ent_row0[e], slot = rb.ent_slot[e];
+    const int ncol = min(SSD_COLS, P - p0);
+    const int per_tok = SSD_COLS + 2 * N + 1;                 // x slice | B | C | raw dt
+    float* stage[2] = {ssm_s, ssm_s + SSD_CH * per_tok};
+    float* sdt = ssm_s + 2 * SSD_CH * per_tok;                // [SSD_CH] dt, [SSD_CH] decay
     float* S = a.ssm_state + (((size_t)slot * a.heads + h) * N) * P;
-    float s[SSD_MAXR];
-    const int nr = (N + SSD_NS - 1) / SSD_NS;
+    float s[SSD_R];
 #pragma unroll
-    for (int i = 0; i < SSD_MAXR; ++i) { const int n = ns + SSD_NS * i; s[i] = (i < nr && n < N && live) ? S[(size_t)n * P + p] : 0.f; }
+    for (int i = 0; i < SSD_R; ++i) { const int n = ns + SSD_NS * i; s[i] = (n < N && live) ? S[(size_t)n * P + p] : 0.f; }
     const float negA = -__expf(a.A_log[h]), Dh = a.D[h], dtb = a.dt_bias[h];
     const int dtcol = 2 * inner + 2 * a.groups * N + h;
-    for (int t = 0; t < len; ++t) {
-        const int r = r0 + t;
-        const float z = a.proj[(size_t)r * a.ldp + dtcol] + dtb;
-        const float dt = (z > 20.f) ? z : log1pf(__expf(z));
-        const float decay = __expf(negA * dt);
-        const float* xr = a.xbc + (size_t)r * C;
-        const float xv = live ? xr[h * P + p] : 0.f;
-        const float* Br = xr + inner + g * N;
-        const float* Cr = Br + a.groups * N;
-        const float dx = dt * xv;
-        float y = 0.f;
-#pragma unroll
-        for (int i = 0; i < SSD_MAXR; ++i) {
-            const int n = ns + SSD_NS * i;
-            if (i < nr && n < N) {
-                s[i] = fmaf(decay, s[i], Br[n] * dx);
-                y = fmaf(s[i], Cr[n], y);
-            }
+    auto fetch = [&](int c, float* dst) {                     // tokens [c * SSD_CH, ...) of the portion
+        const int t0 = c * SSD_CH, nt = min(SSD_CH, len - t0);
+        for (int i = threadIdx.x; i < nt * per_tok; i += blockDim.x) {
+            const int t = i / per_tok, j = i - t * per_tok, r = r0 + t0 + t;
+            const float* src;
+            if (j < SSD_COLS) { if (j >= ncol) continue; src = a.xbc + (size_t)r * C + h * P + p0 + j; }
+            else if (j < SSD_COLS + N) src = a.xbc + (size_t)r * C + inner + g * N + (j - SSD_COLS);
+            else if (j < SSD_COLS + 2 * N) src = a.xbc + (size_t)r * C + inner + (a.groups + g) * N + (j - SSD_COLS - N);
+            else src = a.proj + (size_t)r * a.ldp + dtcol;
+            cp_async4(dst + i, src);
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int nch = (len + SSD_CH - 1) / SSD_CH;
+    fetch(0, stage[0]);
+    for (int c = 0; c < nch; ++c) {
+        if (c + 1 < nch) { fetch(c + 1, stage[(c + 1) & 1]); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const float* st = stage[c & 1];
+        const int nt = min(SSD_CH, len - c * SSD_CH);
+        if (threadIdx.x < nt) {
+            const float z = st[threadIdx.x * per_tok + SSD_COLS + 2 * N] + dtb;
+            const float dt = (z > 20.f) ? z : log1pf(__expf(z));
+            sdt[threadIdx.x] = dt; sdt[SSD_CH + threadIdx.x] = __expf(negA * dt);
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float* tk = st + t * per_tok;
+            const float dt = sdt[t], decay = sdt[SSD_CH + t];
+            const float xv = live ? tk[pl] : 0.f;
+            const float* Br = tk + SSD_COLS;
+            const float* Cr = Br + N;
+            const float dx = dt * xv;
+            float y = 0.f;
 #pragma unroll
-        for (int o = SSD_NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-        if (ns == 0 && live) a.y[(size_t)r * inner + h * P + p] = y + Dh * xv;
+            for (int i = 0; i < SSD_R; ++i) {
+                const int n = ns + SSD_NS * i;
+                if (n < N) {
+                    s[i] = fmaf(decay, s[i], Br[n] * dx);
+                    y = fmaf(s[i], Cr[n], y);
+                }
+            }
+#pragma unroll
+            for (int o = SSD_NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (ns == 0 && live) a.y[(size_t)(r0 + c * SSD_CH + t) * inner + h * P + p] = y + Dh * xv;
+        }
+        __syncthreads();                                      // the stage is free for chunk c + 2
     }
 #pragma unroll
-    for (int i = 0; i < SSD_MAXR; ++i) { const int n = ns + SSD_NS * i; if (i < nr && n < N && live) S[(size_t)n * P + p] = s[i]; }
+    for (int i = 0; i < SSD_R; ++i) { const int n = ns + SSD_NS * i; if (n < N && live) S[(size_t)n * P + p] = s[i]; }
 }
 
 // out = unit_rms_per_group(y * silu(z)) * w : block per (row, group)
@@ -372,7 +467,12 @@ __global__ void moe_sort_kernel(MoeArgs a) {
         *a.n_tiles = t;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) { const int e = a.sel_e[i]; a.sorted[off[e] + atomicAdd(&fill[e], 1)] = i; }
+    for (int e = threadIdx.x; e <= a.E; e += blockDim.x) a.offs[e] = e < a.E ? off[e] : n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = a.sel_e[i], at = off[e] + atomicAdd(&fill[e], 1);
+        a.sorted[at] = i;
+        a.inv[i] = at;
+    }
 }
 
 // Grouped linear: tile = 32 pairs of one expert x 64 output columns.  UP: act[pair] = gelu_erf(up_e h[row of pair]); else y[pair] = down_e act[pair].
@@ -423,12 +523,95 @@ __global__ void __launch_bounds__(256) moe_linear_kernel(MoeArgs a) {
     }
 }
 
-__global__ void moe_combine_kernel(MoeArgs a) {
+// x[r] += sum over the row's choices, in choice order, of weight * expert output (y rows by pair, or by place in the sorted list)
+__global__ void moe_combine_kernel(MoeArgs a, int y_sorted) {
     const int r = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= a.W) return;
     float s = 0.f;
-    for (int k = 0; k < a.top; ++k) s = fmaf(a.sel_w[(size_t)r * a.top + k], a.y[((size_t)r * a.top + k) * a.ldy + c], s);
+    for (int k = 0; k < a.top; ++k) {
+        const int pr = r * a.top + k, row = y_sorted ? a.inv[pr] : pr;
+        s = fmaf(a.sel_w[pr], a.y[(size_t)row * a.ldy + c], s);
+    }
     a.x[(size_t)r * a.ldx + c] += s;
+}
+__global__ void moe_gather_kernel(MoeArgs a, ActOut src, ActOut dst) {
+    const int i = blockIdx.x, r = a.sorted[i] / a.top;
+    const uint4* s = reinterpret_cast<const uint4*>(src.hi + (size_t)r * src.ldb);
+    uint4* d = reinterpret_cast<uint4*>(dst.hi + (size_t)i * dst.ldb);
+    const int n = src.ldb / 8;                              // padded widths: multiples of 8 elements
+    for (int c = threadIdx.x; c < n; c += blockDim.x) d[c] = s[c];
+    if (src.lo_off && dst.lo_off) {
+        const uint4* sl = reinterpret_cast<const uint4*>(src.hi + src.lo_off + (size_t)r * src.ldb);
+        uint4* dl = reinterpret_cast<uint4*>(dst.hi + dst.lo_off + (size_t)i * dst.ldb);
+        for (int c = threadIdx.x; c < n; c += blockDim.x) dl[c] = sl[c];
+    }
+}
+
+constexpr int ARGMAX_PARTS = 64;
+__device__ __forceinline__ void argmax_merge(float& bv, int& bi, float ov, int oi) { if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; } }
+__global__ void __launch_bounds__(256) argmax_parts_kernel(const float* __restrict__ logits, int V, float* __restrict__ pv, int* __restrict__ pi) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const int e = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* row = logits + (size_t)e * V;
+    const int per = (V + ARGMAX_PARTS - 1) / ARGMAX_PARTS, lo = blockIdx.x * per, hi = min(V, lo + per);
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) argmax_merge(bv, bi, row[i], i);
+    for (int o = 16; o > 0; o >>= 1) argmax_merge(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) argmax_merge(bv, bi, sv[w], si[w]);
+        pv[e * ARGMAX_PARTS + blockIdx.x] = bv; pi[e * ARGMAX_PARTS + blockIdx.x] = bi;
+    }
+}
+// one warp per row finishes the argmax (lowest index among maxima), feeds the token back and moves the positions on
+__global__ void greedy_advance_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int E, int* ids, int* row_pos, int* ent_pos0,
+                                      uint32_t* out, int out_stride, int* step) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int t = *step;
+    for (int e = warp; e < E; e += nw) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int i = lane; i < ARGMAX_PARTS; i += 32) argmax_merge(bv, bi, pv[e * ARGMAX_PARTS + i], pi[e * ARGMAX_PARTS + i]);
+        for (int o = 16; o > 0; o >>= 1) argmax_merge(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+        if (lane == 0) {
+            if (bi == 0x7fffffff) bi = 0;
+            out[(size_t)e * out_stride + t] = (uint32_t)bi;
+            ids[e] = bi; row_pos[e] += 1; ent_pos0[e] += 1;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *step = t + 1;
+}
+
+// Experts for a handful of (row, expert) pairs -- a decode step: block = (16 output rows, pair); the pair's input vector sits in
+// shared memory and every warp streams two weight rows with 16-byte loads (padded row widths are multiples of 256).
+template <bool UP>
+__global__ void __launch_bounds__(256) moe_gemv_kernel(MoeArgs a) {
+    extern __shared__ float xs[];
+    const int pr = blockIdx.y, e = a.sel_e[pr], lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int N = UP ? a.F : a.W, K = UP ? a.W : a.F, ldw = UP ? a.ldwu : a.ldwd;
+    const float* x = UP ? a.h + (size_t)(pr / a.top) * a.ldh : a.act + (size_t)pr * a.lda;
+    for (int k = threadIdx.x; k < ldw; k += blockDim.x) xs[k] = k < K ? x[k] : 0.f;
+    __syncthreads();
+    const bf16* Wt = UP ? a.up[e] : a.down[e];
+    for (int rr = 0; rr < 2; ++rr) {
+        const int n = blockIdx.x * 16 + warp * 2 + rr;
+        if (n >= N) continue;
+        const uint4* w8 = reinterpret_cast<const uint4*>(Wt + (size_t)n * ldw);
+        float acc = 0.f;
+        for (int k = lane; k < ldw / 8; k += 32) {
+            const uint4 ww = ldg_stream(w8 + k);
+            const float* xx = xs + 8 * k;
+            acc = fmaf(bf16lo(ww.x), xx[0], acc); acc = fmaf(bf16hi(ww.x), xx[1], acc); acc = fmaf(bf16lo(ww.y), xx[2], acc); acc = fmaf(bf16hi(ww.y), xx[3], acc);
+            acc = fmaf(bf16lo(ww.z), xx[4], acc); acc = fmaf(bf16hi(ww.z), xx[5], acc); acc = fmaf(bf16lo(ww.w), xx[6], acc); acc = fmaf(bf16hi(ww.w), xx[7], acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            if (UP) a.act[(size_t)pr * a.lda + n] = gelu_erf_f(acc);
+            else a.y[(size_t)pr * a.ldy + n] = acc;
+        }
+    }
 }
 
 inline int last_err() { return (int)cudaGetLastError(); }
@@ -443,6 +626,14 @@ int embed_scale_rows_launch(cudaStream_t st, const int* ids, int T, const bf16* 
 int dyt_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, const float* alpha, const float* w, const float* b,
                     const ActOut& out) {
     dyt_rows_kernel<<<R, 128, 0, st>>>(x, ldx, rows, W, alpha, w, b, out);
+    return last_err();
+}
+int greedy_advance_launch(cudaStream_t st, const float* logits, int V, int E, float* part_val, int* part_idx, int* ids, int* row_pos,
+                          int* ent_pos0, uint32_t* out, int out_stride, int* step) {
+    argmax_parts_kernel<<<dim3(ARGMAX_PARTS, E), 256, 0, st>>>(logits, V, part_val, part_idx);
+    int e = last_err();
+    if (e) return e;
+    greedy_advance_kernel<<<1, 256, 0, st>>>(part_val, part_idx, E, ids, row_pos, ent_pos0, out, out_stride, step);
     return last_err();
 }
 int gather_rows_launch(cudaStream_t st, const float* src, int lds, const int* rows, int R, int W, float* dst, int ldd) {
@@ -469,7 +660,8 @@ int sink_attention_launch(cudaStream_t st, const RaggedBatch& rb, const SinkAttn
     else sink_attention_kernel<bf16><<<grid, ATT_WARPS * 32, smem, st>>>(rb, a);
     int e = last_err();
     if (e || a.nsplit == 1) return e;
-    sink_attention_merge_kernel<<<dim3(rb.T, a.H), 64, 0, st>>>(a);
+    if (a.nsplit > 64) return -1000;
+    sink_attention_merge_kernel<<<dim3(rb.T, a.H), 128, 0, st>>>(a);
     return last_err();
 }
 int mamba2_launch_count() { return 4; }
@@ -483,8 +675,14 @@ int mamba2_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba2Args
         conv_window_kernel<<<dim3((C + 127) / 128, rb.E), 128, 0, st>>>(rb, a, C, inner);
         if ((e = last_err())) return e;
     }
-    const int pcols = a.P < 128 ? a.P : 128;
-    ssd_scan_kernel<<<dim3(rb.E, a.heads, (a.P + pcols - 1) / pcols), pcols * SSD_NS, 0, st>>>(rb, a, C);
+    const dim3 sgrid(rb.E, a.heads, (a.P + SSD_COLS - 1) / SSD_COLS);
+    const int nr = (a.N + SSD_NS - 1) / SSD_NS, sthreads = SSD_COLS * SSD_NS;
+    const size_t ssm = (size_t)(2 * SSD_CH * (SSD_COLS + 2 * a.N + 1) + 2 * SSD_CH) * sizeof(float);      // <= 67 KB at N = 256
+    static SmemOptIn seen4, seen8, seen16, seen32;
+    if (nr <= 4) { if ((e = ensure_dyn_smem(ssd_scan_kernel<4>, ssm, seen4))) return e; ssd_scan_kernel<4><<<sgrid, sthreads, ssm, st>>>(rb, a, C); }
+    else if (nr <= 8) { if ((e = ensure_dyn_smem(ssd_scan_kernel<8>, ssm, seen8))) return e; ssd_scan_kernel<8><<<sgrid, sthreads, ssm, st>>>(rb, a, C); }
+    else if (nr <= 16) { if ((e = ensure_dyn_smem(ssd_scan_kernel<16>, ssm, seen16))) return e; ssd_scan_kernel<16><<<sgrid, sthreads, ssm, st>>>(rb, a, C); }
+    else { if ((e = ensure_dyn_smem(ssd_scan_kernel<32>, ssm, seen32))) return e; ssd_scan_kernel<32><<<sgrid, sthreads, ssm, st>>>(rb, a, C); }
     if ((e = last_err())) return e;
     gated_group_rms_kernel<<<dim3(rb.T, a.norm_groups), 128, 0, st>>>(a);
     return last_err();
@@ -493,18 +691,37 @@ int clamped_glu_launch(cudaStream_t st, const float* gu, int ld, int up_off, int
     clamped_glu_kernel<<<dim3((F + 127) / 128, T), 128, 0, st>>>(gu, ld, up_off, F, limit, out);
     return last_err();
 }
-int moe_launch(cudaStream_t st, const MoeArgs& a) {
+int moe_route_launch(cudaStream_t st, const MoeArgs& a) {
     if (a.E > 256 || a.top > a.E || a.top < 1) return -1000;
     route_kernel<<<(a.T + 3) / 4, 128, 0, st>>>(a);
     int e = last_err();
     if (e) return e;
     moe_sort_kernel<<<1, 1024, (size_t)3 * a.E * sizeof(int), st>>>(a);
-    if ((e = last_err())) return e;
+    return last_err();
+}
+int moe_experts_launch(cudaStream_t st, const MoeArgs& a) {
+    if (a.T * a.top <= 32 && (a.ldwu & 255) == 0 && (a.ldwd & 255) == 0 && (size_t)std::max(a.ldwu, a.ldwd) * 4 <= 48 * 1024) {
+        moe_gemv_kernel<true><<<dim3((a.F + 15) / 16, a.T * a.top), 256, (size_t)a.ldwu * 4, st>>>(a);
+        int e = last_err();
+        if (e) return e;
+        moe_gemv_kernel<false><<<dim3((a.W + 15) / 16, a.T * a.top), 256, (size_t)a.ldwd * 4, st>>>(a);
+        if ((e = last_err())) return e;
+        return moe_combine_launch(st, a, false);
+    }
     moe_linear_kernel<true><<<dim3((a.F + 63) / 64, a.max_tiles), 256, 0, st>>>(a);
-    if ((e = last_err())) return e;
+    int e = last_err();
+    if (e) return e;
     moe_linear_kernel<false><<<dim3((a.W + 63) / 64, a.max_tiles), 256, 0, st>>>(a);
     if ((e = last_err())) return e;
-    moe_combine_kernel<<<dim3((a.W + 127) / 128, a.T), 128, 0, st>>>(a);
+    return moe_combine_launch(st, a, false);
+}
+int moe_gather_launch(cudaStream_t st, const MoeArgs& a, const ActOut& src, const ActOut& dst) {
+    if (!src.hi || !dst.hi || src.ldb != dst.ldb || (src.ldb & 7)) return -1000;
+    moe_gather_kernel<<<a.T * a.top, 128, 0, st>>>(a, src, dst);
+    return last_err();
+}
+int moe_combine_launch(cudaStream_t st, const MoeArgs& a, bool y_sorted) {
+    moe_combine_kernel<<<dim3((a.W + 127) / 128, a.T), 128, 0, st>>>(a, y_sorted ? 1 : 0);
     return last_err();
 }
 

@@ -42,9 +42,9 @@ struct AttnPrepArgs {
     int H, G, d, dv;
     float eps;
     float temp_coef; int temp_every;  // temp_every <= 0: no query temperature
-    float* q_out; int ldq;            // [T, H * d] normalised, temperature applied
-    void* k_pool; void* v_pool;       // pages [n_pages, G, KV_PAGE, d | dv] of f32 or bf16
-    int kv_f32;
+    ActOut q_out;                     // [T, H * d] normalised, temperature applied (f32 for sink_attention, planes for the flash kernel)
+    void* k_pool; void* v_pool;       // pages [n_pages, G, KV_PAGE, d | dv] of f32, or of bf16 with an optional low-order plane
+    int kv_f32; long long kv_lo_off;  // bf16 pages: element offset of the plane holding bf16(x - bf16(x)), 0 = none
     int has_kv;
     const int* block_table; int max_pages;
 };
@@ -52,7 +52,7 @@ int attn_prep_launch(cudaStream_t st, const RaggedBatch& rb, const AttnPrepArgs&
 
 struct SinkAttnArgs {
     const float* q; int ldq;          // [T, H * d]
-    const void* k_pool; const void* v_pool; int kv_f32;
+    const void* k_pool; const void* v_pool; int kv_f32; long long kv_lo_off;
     const int* block_table; int max_pages;
     int H, G, d, dv;
     float scale;
@@ -91,13 +91,27 @@ struct MoeArgs {
     int ldwu, ldwd;
     int* sel_e; float* sel_w;         // [T * top]
     int* sorted; int* tile_e; int* tile_r0; int* tile_n; int* n_tiles; int max_tiles;
+    int* inv;                         // [T * top] place of each pair in `sorted`
+    int* offs;                        // [E + 1] first place of each expert's pairs in `sorted`
     float* act; int lda;              // [T * top, lda]
     float* y; int ldy;                // [T * top, ldy]
     float* x; int ldx;                // residual, += sum_k w_k y_k
 };
-int moe_launch(cudaStream_t st, const MoeArgs& a);
+// router softmax + top-k, then the counting sort by expert (2 launches)
+int moe_route_launch(cudaStream_t st, const MoeArgs& a);
+// experts as grouped f32 linears over the sorted pairs + the ordered combine into x (3 launches): y rows indexed by pair
+int moe_experts_launch(cudaStream_t st, const MoeArgs& a);
+// tensor-core expert path: rows of `src` (bf16 planes) gathered into expert order, dense GEMMs per expert by the caller (y rows in
+// sorted order), then the combine through `inv`
+int moe_gather_launch(cudaStream_t st, const MoeArgs& a, const ActOut& src, const ActOut& dst);
+int moe_combine_launch(cudaStream_t st, const MoeArgs& a, bool y_sorted);
 inline int moe_max_tiles(int T, int top, int E) { return (T * top + 31) / 32 + E; }
 
+// Greedy feedback for on-device decode loops: token = argmax of logits row e (lowest index among maxima; 64 partial results per
+// row in part_val / part_idx, then one block) -> ids[e], recorded at out[e * out_stride + *step]; row_pos[e] and ent_pos0[e] move on
+// by one; *step is bumped once.
+int greedy_advance_launch(cudaStream_t st, const float* logits, int V, int E, float* part_val, int* part_idx, int* ids, int* row_pos,
+                          int* ent_pos0, uint32_t* out, int out_stride, int* step);
 int gather_rows_launch(cudaStream_t st, const float* src, int lds, const int* rows, int R, int W, float* dst, int ldd);
 
 }  // namespace cb

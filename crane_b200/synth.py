@@ -332,7 +332,70 @@ def qwen3_tts_tensor_specs(cfg: dict):
         yield "talker.code_predictor.small_to_mtp_projection.bias", (cp["hidden_size"],), "bias"
 
 
+# --------------------------------------------------------------------------------------
+# Fosovik: layer-list decoder (config.json carries "architecture": "Fosovik" and the list of layers)
+# --------------------------------------------------------------------------------------
+def fosovik_config(width=1024, vocab=248320, blocks=6, attn_every=4, heads=8, kv_heads=2, dim=256, ssm_heads=16, ssm_vdim=128, state=128,
+                   groups=2, conv=4, ff=3584, moe=None, limit=7.0):
+    """`blocks` groups of (attn_every - 1) Mamba-2 layers and one sink-attention layer, every layer with a feed-forward: the shape
+    of the Qwen3.5 hybrid at the same width, so the two can be timed side by side.  moe = (experts, top, expert_ff) or None (dense)."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}}
+    ssm = {"heads": ssm_heads, "vdim": ssm_vdim, "state": state, "groups": groups, "conv": conv, "norm_groups": ssm_heads}
+    mlp = ({"kind": "moe", "expert": {"ff": moe[2]}, "router": {"experts": moe[0], "top": moe[1]}} if moe else
+           {"kind": "dense", "ff": ff, "limit": limit})
+    layers = []
+    for _ in range(blocks):
+        layers += [{"type": "mamba2", "mixer": dict(ssm), "mlp": dict(mlp)} for _ in range(attn_every - 1)]
+        layers.append({"type": "attention", "mixer": dict(att), "mlp": dict(mlp)})
+    return {"architecture": "Fosovik", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def fosovik_tensor_specs(cfg: dict):
+    """(name, shape, kind) of every tensor: 'l<i>.norm1[.b|.alpha]', 'l<i>.mix.*', 'l<i>.mlp.*', 'embed', 'head', 'final.norm*'."""
+    W, V = cfg["width"], cfg["vocab"]
+    yield "embed", (V, W), "embed"
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        yield p + "norm1", (W,), "norm"
+        yield p + "norm1.b", (W,), "bias"
+        yield p + "norm1.alpha", (), "alpha"
+        if L["type"] == "attention":
+            yield p + "mix.q", (m["heads"] * m["dim"], W), "linear"
+            if m.get("kv_from") is None:
+                yield p + "mix.k", (m["kv_heads"] * m["dim"], W), "linear"
+                yield p + "mix.v", (m["kv_heads"] * m["vdim"], W), "linear"
+            yield p + "mix.sink", (m["heads"],), "bias"
+            yield p + "mix.o", (W, m["heads"] * m["vdim"]), "linear"
+        else:
+            inner, gn = m["heads"] * m["vdim"], m["groups"] * m["state"]
+            yield p + "mix.in", (2 * inner + 2 * gn + m["heads"], W), "linear"
+            yield p + "mix.conv", (inner + 2 * gn, m["conv"]), "linear"
+            yield p + "mix.conv.b", (inner + 2 * gn,), "bias"
+            yield p + "mix.dt_bias", (m["heads"],), "dt_bias"
+            yield p + "mix.A_log", (m["heads"],), "a_log"
+            yield p + "mix.D", (m["heads"],), "norm"
+            yield p + "mix.norm", (inner,), "norm"
+            yield p + "mix.o", (W, inner), "linear"
+        f = L.get("mlp")
+        if f and f["kind"] == "dense":
+            yield p + "mlp.gate", (f["ff"], W), "linear"
+            yield p + "mlp.up", (f["ff"], W), "linear"
+            yield p + "mlp.down", (W, f["ff"]), "linear"
+        elif f:
+            for e in range(f["router"]["experts"]):
+                yield f"{p}mlp.e{e}.up", (f["expert"]["ff"], W), "linear"
+                yield f"{p}mlp.e{e}.down", (W, f["expert"]["ff"]), "linear"
+            yield p + "mlp.router", (f["router"]["experts"], W), "linear"
+    yield "final.norm", (W,), "norm"
+    yield "final.norm.b", (W,), "bias"
+    yield "final.norm.alpha", (), "alpha"
+    yield "head", (V, W), "linear"
+
+
 def tensor_specs(cfg: dict):
+    if cfg.get("architecture") == "Fosovik":
+        yield from fosovik_tensor_specs(cfg)
+        return
     if cfg.get("model_type") == "qwen3_tts":
         yield from qwen3_tts_tensor_specs(cfg)
         return
@@ -364,6 +427,8 @@ def make_tensor(name: str, shape, kind: str) -> np.ndarray:
         x = _normal(name, shape, 1.0)
     elif kind == "bias":
         x = _normal(name, shape, 0.02)
+    elif kind == "alpha":      # Dynamic-Tanh slope: a scalar near one half
+        x = _normal(name, shape, 0.02, 0.5)
     else:
         raise ValueError(kind)
     return bf16_round(x)

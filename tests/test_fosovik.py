@@ -347,3 +347,57 @@ def test_model_folder_loader_and_trace_runner(tmp_path):
         rd = lambda i: np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)
         assert rel(rd(0), wa[[0, 69]]) < tol and rel(rd(1), wa[[70]]) < tol
         assert rel(rd(2), np.stack([wa[74], wb[19]])) < tol and rel(rd(3), wb[[19]]) < tol
+
+
+# ---------------------------------------------------------------------------------------------------- the wide paths
+ATT_W = {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 128, "vdim": 128, "scale": 0.45,
+                                        "q_temp": {"coef": 0.3, "every": 32}}, "mlp": None}
+SSM_W = {"type": "mamba2", "mixer": {"heads": 4, "vdim": 64, "state": 64, "groups": 2, "conv": 4, "norm_groups": 4}, "mlp": None}
+MOE_W = {"kind": "moe", "expert": {"ff": 96}, "router": {"experts": 4, "top": 2}}
+WIDE = config([layer(ATT_W, MOE_W), layer(SSM_W, DENSE), layer(ATT_W, DENSE, kv_from=0)], width=256, vocab=512)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("precision,tol", [("split", SPLIT_TOL), ("f32", F32_TOL)])
+def test_tensor_core_attention_and_expert_gemms(precision, tol):
+    """128-wide heads and enough (row, expert) pairs: the serving precisions take the flash kernel (sink, per-sequence pages and
+    offsets) and per-expert tensor-core GEMMs; the exact mode stays on the f32 kernels.  Both against the oracle."""
+    m, o = make(WIDE, 61, precision=precision, max_tokens=1024)
+    a, b = tokens(400, WIDE["vocab"], 62), tokens(150, WIDE["vocab"], 63)
+    wa, wb = o.forward(a, o.new_state()).numpy(), o.forward(b, o.new_state()).numpy()
+    got = m.step_batch([(0, a[:300], all_rows(300))])                 # 600 pairs: expert GEMMs; 300 rows: flash
+    assert rel(got, wa[:300]) < tol
+    s1 = m.seq_create()
+    got = m.step_batch([(0, a[300:], all_rows(100)), (s1, b[:149], all_rows(149))])   # cached prefix + a second sequence, ragged
+    assert rel(got[:100], wa[300:]) < tol and rel(got[100:], wb[:149]) < tol
+    got = m.step_batch([(s1, b[149:], [0])])
+    assert rel(got, wb[149:]) < tol
+    m.close()
+
+
+@pytest.mark.gpu
+def test_on_device_greedy_loop_equals_step_by_step():
+    m, o = make(FULL, 71, precision="f32", max_tokens=1024)
+    pa, pb = tokens(50, FULL["vocab"], 72), tokens(70, FULL["vocab"], 73)
+
+    def by_steps(p, n):
+        m.clear_kv_cache()
+        lg = m.step_batch([(0, p, [len(p) - 1])])
+        out = []
+        for _ in range(n):
+            out.append(int(lg[0].argmax()))
+            lg = m.step_batch([(0, [out[-1]], [0])])
+        return out
+
+    wa, wb = by_steps(pa, 40), by_steps(pb, 40)
+    m.clear_kv_cache()
+    assert m.generate(pa, max_new_tokens=40).tolist() == wa         # prefill + 39 replays of the decode graph across a page border
+    m.clear_kv_cache()
+    s1 = m.seq_create()
+    m.step_batch([(0, pa, []), (s1, pb, [])])
+    toks, lg = m.decode_batch([0, s1], [wa[0], wb[0]], n_steps=30, want_logits=True)
+    assert toks[0].tolist() == wa[1:31] and toks[1].tolist() == wb[1:31]
+    st = o.new_state(); ref = o.forward(pb + wb[:30], st).numpy()[-1]
+    assert rel(lg[1], ref) < F32_TOL
+    assert m.seq_len(s1) == 100 and m.kv_len() == 80
+    m.close()

@@ -28,6 +28,8 @@ def cheap(shape, kind):
         return np.ones(shape, np.float32)
     if kind in ("norm0", "bias", "dt_bias"):
         return np.zeros(shape, np.float32)
+    if kind == "alpha":
+        return np.full(shape, 0.5, np.float32)
     if kind == "a_log":
         return np.full(shape, -2.0, np.float32)
     reps = (n + BLOCK.size - 1) // BLOCK.size
