@@ -135,131 +135,154 @@ __global__ void attn_prep_kernel(RaggedBatch rb, AttnPrepArgs a) {
 constexpr int ATT_WARPS = 4;
 constexpr int ATT_MAXC = 8;      // value columns per lane: dv <= 256
 
-// Block = (row, head, split); its warps walk 32-key tiles of the split's key range, one key per lane for the scores, one value
-// column set per lane for the weighted sum, online softmax per warp; warps, then splits, merge in a fixed order.
-template <typename KT>
+// Block = (row, group of up to REP query heads that share one key/value head, split).  Its warps walk 32-key tiles of the split's
+// key range: one key per lane for the scores -- the key is fetched and widened once and multiplied into every query head of the
+// group -- then eight contiguous value columns per lane for the weighted sums, online softmax per warp and head; warps, then
+// splits, merge in a fixed order.  Widths that are not multiples of 8 take the element-wise loads.
+template <typename KT> __device__ __forceinline__ void kv_load8(const KT* p, long long lo, float* v);
+template <> __device__ __forceinline__ void kv_load8<float>(const float* p, long long, float* v) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void kv_load8<bf16>(const bf16* p, long long lo, float* v) {
+    const uint4 h = *reinterpret_cast<const uint4*>(p);
+    v[0] = bf16lo(h.x); v[1] = bf16hi(h.x); v[2] = bf16lo(h.y); v[3] = bf16hi(h.y);
+    v[4] = bf16lo(h.z); v[5] = bf16hi(h.z); v[6] = bf16lo(h.w); v[7] = bf16hi(h.w);
+    if (lo) {
+        const uint4 l = *reinterpret_cast<const uint4*>(p + lo);
+        v[0] += bf16lo(l.x); v[1] += bf16hi(l.x); v[2] += bf16lo(l.y); v[3] += bf16hi(l.y);
+        v[4] += bf16lo(l.z); v[5] += bf16hi(l.z); v[6] += bf16lo(l.w); v[7] += bf16hi(l.w);
+    }
+}
+template <typename KT, int REP>
 __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBatch rb, SinkAttnArgs a) {
-    extern __shared__ float smem[];
-    float* sq = smem;                                   // [d]
-    float* sm = sq + a.d;                               // [ATT_WARPS] m, [ATT_WARPS] l, [ATT_WARPS, dv] acc
-    const int r = blockIdx.x, h = blockIdx.y, sp = blockIdx.z, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    extern __shared__ __align__(16) float smem[];
+    const int d = a.d, dv = a.dv, rep = a.H / a.G, nb = (rep + REP - 1) / REP;
+    float* sq = smem;                                   // [REP][d]
+    float* wm = sq + REP * d;                           // [ATT_WARPS][REP] m, then l, then [ATT_WARPS][REP][dv] acc
+    float* wl = wm + ATT_WARPS * REP;
+    float* wa = wl + ATT_WARPS * REP;
+    const int r = blockIdx.x, sp = blockIdx.z, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = blockIdx.y / nb, h0 = g * rep + (blockIdx.y % nb) * REP, nh = min(REP, (g + 1) * rep - h0);
     const int e = rb.row_entry[r], pos = rb.row_pos[r], slot = rb.ent_slot[e];
-    const int g = h / (a.H / a.G), d = a.d, dv = a.dv;
     const int* bt = a.block_table + (size_t)slot * a.max_pages;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) sq[c] = a.q[(size_t)r * a.ldq + (size_t)h * d + c] * a.scale;
+    for (int i = threadIdx.x; i < nh * d; i += blockDim.x) sq[i] = a.q[(size_t)r * a.ldq + (size_t)h0 * d + i] * a.scale;
     __syncthreads();
     const int nkeys = pos + 1;
     const int ntiles = (nkeys + 31) / 32, per = (ntiles + a.nsplit - 1) / a.nsplit;
     const int t_lo = sp * per, t_hi = min(ntiles, t_lo + per);
-    float m = -INFINITY, l = 0.f, acc[ATT_MAXC];
+    float m[REP], l[REP], acc[REP][ATT_MAXC];
 #pragma unroll
-    for (int c = 0; c < ATT_MAXC; ++c) acc[c] = 0.f;
-    const bool vec = sizeof(KT) == 4 ? (d & 3) == 0 : (d & 7) == 0;
-    const bool vvec = (dv & 7) == 0;        // value columns 8 * lane .. 8 * lane + 7 per lane (16-byte loads) instead of lane + 32 c
+    for (int q = 0; q < REP; ++q) {
+        m[q] = -INFINITY; l[q] = 0.f;
+#pragma unroll
+        for (int c = 0; c < ATT_MAXC; ++c) acc[q][c] = 0.f;
+    }
+    const bool kvec = (d & 7) == 0, vvec = (dv & 7) == 0;
     for (int t = t_lo + warp; t < t_hi; t += ATT_WARPS) {
         const int j = t * 32 + lane;
         const int pg = bt[(t * 32) / KV_PAGE];           // a 32-key tile never straddles a 64-token page
         const size_t base = ((size_t)pg * a.G + g) * KV_PAGE + ((t * 32) % KV_PAGE);
-        float s = -INFINITY;
+        float sc[REP];
+#pragma unroll
+        for (int q = 0; q < REP; ++q) sc[q] = 0.f;
         if (j < nkeys) {
             const KT* kr = (const KT*)a.k_pool + (base + lane) * d;
-            float dot = 0.f;
-            if (vec && sizeof(KT) == 4) {
-                const float4* k4 = reinterpret_cast<const float4*>(kr);
-                for (int c = 0; c < d / 4; ++c) {
-                    const float4 kk = k4[c];
-                    dot = fmaf(sq[4 * c], kk.x, dot); dot = fmaf(sq[4 * c + 1], kk.y, dot);
-                    dot = fmaf(sq[4 * c + 2], kk.z, dot); dot = fmaf(sq[4 * c + 3], kk.w, dot);
-                }
-            } else if (vec) {                            // 8 bf16 per 16-byte load, the low-order plane added as it comes
-                const uint4* k8 = reinterpret_cast<const uint4*>(kr);
-                const uint4* l8 = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(kr) + a.kv_lo_off);
-                for (int c = 0; c < d / 8; ++c) {
-                    const uint4 kk = k8[c];
-                    float k0 = bf16lo(kk.x), k1 = bf16hi(kk.x), k2 = bf16lo(kk.y), k3 = bf16hi(kk.y);
-                    float k4 = bf16lo(kk.z), k5 = bf16hi(kk.z), k6 = bf16lo(kk.w), k7 = bf16hi(kk.w);
-                    if (a.kv_lo_off) {
-                        const uint4 ll = l8[c];
-                        k0 += bf16lo(ll.x); k1 += bf16hi(ll.x); k2 += bf16lo(ll.y); k3 += bf16hi(ll.y);
-                        k4 += bf16lo(ll.z); k5 += bf16hi(ll.z); k6 += bf16lo(ll.w); k7 += bf16hi(ll.w);
+            if (kvec) {
+                for (int c = 0; c < d; c += 8) {
+                    float kf[8];
+                    kv_load8<KT>(kr + c, a.kv_lo_off, kf);
+#pragma unroll
+                    for (int q = 0; q < REP; ++q) {
+                        if (q < nh) {
+                            const float4 qa = *reinterpret_cast<const float4*>(sq + q * d + c), qb = *reinterpret_cast<const float4*>(sq + q * d + c + 4);
+                            float x = sc[q];
+                            x = fmaf(qa.x, kf[0], x); x = fmaf(qa.y, kf[1], x); x = fmaf(qa.z, kf[2], x); x = fmaf(qa.w, kf[3], x);
+                            x = fmaf(qb.x, kf[4], x); x = fmaf(qb.y, kf[5], x); x = fmaf(qb.z, kf[6], x); x = fmaf(qb.w, kf[7], x);
+                            sc[q] = x;
+                        }
                     }
-                    const float* qq = sq + 8 * c;
-                    dot = fmaf(qq[0], k0, dot); dot = fmaf(qq[1], k1, dot); dot = fmaf(qq[2], k2, dot); dot = fmaf(qq[3], k3, dot);
-                    dot = fmaf(qq[4], k4, dot); dot = fmaf(qq[5], k5, dot); dot = fmaf(qq[6], k6, dot); dot = fmaf(qq[7], k7, dot);
                 }
             } else {
-                for (int c = 0; c < d; ++c) dot = fmaf(sq[c], kv_load<KT>(kr + c, a.kv_lo_off), dot);
-            }
-            s = dot;
-        }
-        const float tm = warp_max(s);
-        const float mn = fmaxf(m, tm);
-        const float corr = (m == -INFINITY) ? 0.f : __expf(m - mn);
-        const float p = (j < nkeys) ? __expf(s - mn) : 0.f;
-        l = l * corr + warp_sum(p);
+                for (int c = 0; c < d; ++c) {
+                    const float kf = kv_load<KT>(kr + c, a.kv_lo_off);
 #pragma unroll
-        for (int c = 0; c < ATT_MAXC; ++c) acc[c] *= corr;
-        m = mn;
+                    for (int q = 0; q < REP; ++q) if (q < nh) sc[q] = fmaf(sq[q * d + c], kf, sc[q]);
+                }
+            }
+        }
+        float p[REP];
+#pragma unroll
+        for (int q = 0; q < REP; ++q) {
+            const float sv = (j < nkeys) ? sc[q] : -INFINITY;
+            const float mn = fmaxf(m[q], warp_max(sv));
+            const float corr = (m[q] == -INFINITY) ? 0.f : __expf(m[q] - mn);
+            p[q] = (j < nkeys) ? __expf(sv - mn) : 0.f;
+            l[q] = l[q] * corr + warp_sum(p[q]);
+#pragma unroll
+            for (int c = 0; c < ATT_MAXC; ++c) acc[q][c] *= corr;
+            m[q] = mn;
+        }
         const int cnt = min(32, nkeys - t * 32);
         const KT* vb = (const KT*)a.v_pool + base * dv;
         if (vvec) {
             const bool mine = 8 * lane < dv;
             for (int jj = 0; jj < cnt; ++jj) {
-                const float pj = __shfl_sync(0xffffffffu, p, jj);
-                if (!mine) continue;
                 float v[8];
-                if (sizeof(KT) == 4) {
-                    const float4* v4 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(vb) + (size_t)jj * dv + 8 * lane);
-                    const float4 x0 = v4[0], x1 = v4[1];
-                    v[0] = x0.x; v[1] = x0.y; v[2] = x0.z; v[3] = x0.w; v[4] = x1.x; v[5] = x1.y; v[6] = x1.z; v[7] = x1.w;
-                } else {
-                    const bf16* vp = reinterpret_cast<const bf16*>(vb) + (size_t)jj * dv + 8 * lane;
-                    const uint4 hh = *reinterpret_cast<const uint4*>(vp);
-                    v[0] = bf16lo(hh.x); v[1] = bf16hi(hh.x); v[2] = bf16lo(hh.y); v[3] = bf16hi(hh.y);
-                    v[4] = bf16lo(hh.z); v[5] = bf16hi(hh.z); v[6] = bf16lo(hh.w); v[7] = bf16hi(hh.w);
-                    if (a.kv_lo_off) {
-                        const uint4 ll = *reinterpret_cast<const uint4*>(vp + a.kv_lo_off);
-                        v[0] += bf16lo(ll.x); v[1] += bf16hi(ll.x); v[2] += bf16lo(ll.y); v[3] += bf16hi(ll.y);
-                        v[4] += bf16lo(ll.z); v[5] += bf16hi(ll.z); v[6] += bf16lo(ll.w); v[7] += bf16hi(ll.w);
+                if (mine) kv_load8<KT>(vb + (size_t)jj * dv + 8 * lane, a.kv_lo_off, v);
+#pragma unroll
+                for (int q = 0; q < REP; ++q) {
+                    const float pj = __shfl_sync(0xffffffffu, p[q], jj);
+                    if (mine && q < nh) {
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) acc[q][c] = fmaf(pj, v[c], acc[q][c]);
                     }
                 }
-#pragma unroll
-                for (int c = 0; c < 8; ++c) acc[c] = fmaf(pj, v[c], acc[c]);
             }
         } else {
             for (int jj = 0; jj < cnt; ++jj) {
-                const float pj = __shfl_sync(0xffffffffu, p, jj);
+                float v[ATT_MAXC];
 #pragma unroll
-                for (int c = 0; c < ATT_MAXC; ++c) {
-                    const int col = lane + 32 * c;
-                    if (col < dv) acc[c] = fmaf(pj, kv_load<KT>(vb + (size_t)jj * dv + col, a.kv_lo_off), acc[c]);
+                for (int c = 0; c < ATT_MAXC; ++c) { const int col = lane + 32 * c; v[c] = col < dv ? kv_load<KT>(vb + (size_t)jj * dv + col, a.kv_lo_off) : 0.f; }
+#pragma unroll
+                for (int q = 0; q < REP; ++q) {
+                    const float pj = __shfl_sync(0xffffffffu, p[q], jj);
+#pragma unroll
+                    for (int c = 0; c < ATT_MAXC; ++c) acc[q][c] = fmaf(pj, v[c], acc[q][c]);
                 }
             }
         }
     }
-    // merge the warps in warp order
-    float* wm = sm; float* wl = sm + ATT_WARPS; float* wa = sm + 2 * ATT_WARPS;
-    if (lane == 0) { wm[warp] = m; wl[warp] = l; }
+    // merge the warps in warp order, head by head
 #pragma unroll
-    for (int c = 0; c < ATT_MAXC; ++c) { const int col = vvec ? 8 * lane + c : lane + 32 * c; if (col < dv) wa[warp * dv + col] = acc[c]; }
-    __syncthreads();
-    float M = -INFINITY;
-    for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, wm[w]);
-    const bool last = a.nsplit == 1;
-    const float sink = (last && a.sink) ? a.sink[h] : -INFINITY;
-    const float Mx = fmaxf(M, sink);
-    float Lsum = (sink == -INFINITY) ? 0.f : __expf(sink - Mx);
-    float wsc[ATT_WARPS];
-    for (int w = 0; w < ATT_WARPS; ++w) { wsc[w] = (wm[w] == -INFINITY) ? 0.f : __expf(wm[w] - Mx); Lsum += wl[w] * wsc[w]; }
-    for (int col = threadIdx.x; col < dv; col += blockDim.x) {
-        float o = 0.f;
-        for (int w = 0; w < ATT_WARPS; ++w) o += wa[w * dv + col] * wsc[w];
-        if (last) store_act(a.out, r, h * dv + col, o / Lsum);
-        else a.part[(((size_t)r * a.H + h) * a.nsplit + sp) * (dv + 2) + 2 + col] = o;
+    for (int q = 0; q < REP; ++q) {
+        if (q < nh) {
+            if (lane == 0) { wm[warp * REP + q] = m[q]; wl[warp * REP + q] = l[q]; }
+#pragma unroll
+            for (int c = 0; c < ATT_MAXC; ++c) { const int col = vvec ? 8 * lane + c : lane + 32 * c; if (col < dv) wa[((size_t)warp * REP + q) * dv + col] = acc[q][c]; }
+        }
     }
-    if (!last && threadIdx.x == 0) {
-        float* pp = a.part + (((size_t)r * a.H + h) * a.nsplit + sp) * (dv + 2);
-        pp[0] = Mx; pp[1] = Lsum;          // (no sink yet: Mx == M, possibly -inf for an empty split)
+    __syncthreads();
+    const bool last = a.nsplit == 1;
+    for (int q = 0; q < nh; ++q) {
+        const int h = h0 + q;
+        float M = -INFINITY;
+        for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, wm[w * REP + q]);
+        const float sink = (last && a.sink) ? a.sink[h] : -INFINITY;
+        const float Mx = fmaxf(M, sink);
+        float Lsum = (sink == -INFINITY) ? 0.f : __expf(sink - Mx);
+        float wsc[ATT_WARPS];
+        for (int w = 0; w < ATT_WARPS; ++w) { wsc[w] = (wm[w * REP + q] == -INFINITY) ? 0.f : __expf(wm[w * REP + q] - Mx); Lsum += wl[w * REP + q] * wsc[w]; }
+        for (int col = threadIdx.x; col < dv; col += blockDim.x) {
+            float o = 0.f;
+            for (int w = 0; w < ATT_WARPS; ++w) o += wa[((size_t)w * REP + q) * dv + col] * wsc[w];
+            if (last) store_act(a.out, r, h * dv + col, o / Lsum);
+            else a.part[(((size_t)r * a.H + h) * a.nsplit + sp) * (dv + 2) + 2 + col] = o;
+        }
+        if (!last && threadIdx.x == 0) {
+            float* pp = a.part + (((size_t)r * a.H + h) * a.nsplit + sp) * (dv + 2);
+            pp[0] = Mx; pp[1] = Lsum;          // (no sink yet: Mx == M, possibly -inf for an empty split)
+        }
     }
 }
 
@@ -305,6 +328,22 @@ __global__ void conv_silu_kernel(RaggedBatch rb, Mamba2Args a, int C, int col0) 
     }
     a.xbc[(size_t)r * C + c] = acc / (1.f + __expf(-acc));
 }
+// Every entry one token (decode): the convolution and the window shift in one pass; thread = (entry, channel) owns its window column.
+__global__ void conv_step_kernel(RaggedBatch rb, Mamba2Args a, int C, int col0) {
+    const int e = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int r = rb.ent_row0[e], slot = rb.ent_slot[e], taps = a.taps;
+    float* win = a.conv_state + (size_t)slot * (taps - 1) * C;
+    const float u = a.proj[(size_t)r * a.ldp + col0 + c];
+    float acc = fmaf(a.conv_w[(size_t)c * taps + taps - 1], u, a.conv_b[c]);
+    for (int k = 0; k < taps - 1; ++k) {
+        const float w = win[(size_t)k * C + c];
+        acc = fmaf(a.conv_w[(size_t)c * taps + k], w, acc);
+        if (k > 0) win[(size_t)(k - 1) * C + c] = w;
+    }
+    if (taps > 1) win[(size_t)(taps - 2) * C + c] = u;
+    a.xbc[(size_t)r * C + c] = acc / (1.f + __expf(-acc));
+}
 // New window = the last taps-1 inputs of the sequence (older ones shift down when the entry is shorter than the window).
 __global__ void conv_window_kernel(RaggedBatch rb, Mamba2Args a, int C, int col0) {
     const int e = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -322,38 +361,69 @@ __global__ void conv_window_kernel(RaggedBatch rb, Mamba2Args a, int C, int col0
 // operand fetch, so the step inputs (x slice, B, C, dt) of SSD_CH tokens at a time are staged in shared memory with cp.async,
 // double-buffered: chunk c + 1 is in flight while chunk c is consumed.  dt = softplus(.) and the decay exp(-exp(A) dt) are
 // computed once per token, in f32, when its chunk lands.
-constexpr int SSD_NS = 8, SSD_MAXR = 32, SSD_COLS = 32, SSD_CH = 16;      // N <= 256; 32 columns x 8 = 256 threads per block
+constexpr int SSD_NS = 8, SSD_MAXR = 32, SSD_COLS = 16, SSD_CH = 16;      // N <= 256; 16 columns x 8 = 128 threads per block: one warp per scheduler, many blocks
+__device__ __forceinline__ void cp_async16s(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
 }
+// Staged layout of one token: x slice [SSD_COLS] | B | C | dt, pad.  Thread ns owns the CONTIGUOUS state rows ns * R .. ns * R + R - 1,
+// so it reads its B and C values as float4; every R-run is followed by 4 pad floats, which spreads the eight runs of a warp over
+// all banks.
+__host__ __device__ inline int ssd_idx(int n, int R) { return n + 4 * (n / R); }
+__host__ __device__ inline int ssd_npad(int N, int R) { (void)N; return 8 * (R + 4); }      // all eight runs, whatever N: no bounds checks in the loop
 template <int SSD_R>                                         // state rows per thread: ceil(N / 8) rounded up to 4, 8, 16 or 32
 __global__ void __launch_bounds__(SSD_COLS * SSD_NS) ssd_scan_kernel(RaggedBatch rb, Mamba2Args a, int C) {
-    extern __shared__ float ssm_s[];
+    extern __shared__ __align__(16) float ssm_s[];
     const int e = blockIdx.x, h = blockIdx.y, ns = threadIdx.x & (SSD_NS - 1), pl = threadIdx.x / SSD_NS;
     const int p0 = blockIdx.z * SSD_COLS, p = p0 + pl;
     const int P = a.P, N = a.N, inner = a.heads * P, g = h / (a.heads / a.groups);
     const bool live = p < P;
     const int len = rb.ent_len[e], r0 = rb.ent_row0[e], slot = rb.ent_slot[e];
     const int ncol = min(SSD_COLS, P - p0);
-    const int per_tok = SSD_COLS + 2 * N + 1;                 // x slice | B | C | raw dt
+    const int NP = ssd_npad(N, SSD_R), per_tok = SSD_COLS + 2 * NP + 4;
     float* stage[2] = {ssm_s, ssm_s + SSD_CH * per_tok};
     float* sdt = ssm_s + 2 * SSD_CH * per_tok;                // [SSD_CH] dt, [SSD_CH] decay
     float* S = a.ssm_state + (((size_t)slot * a.heads + h) * N) * P;
+    const int n0 = ns * SSD_R;
+    // rows past N and tokens past the portion's end multiply zeros: the stages start zeroed and only real values are ever copied in
+    for (int i = threadIdx.x; i < 2 * SSD_CH * per_tok; i += blockDim.x) ssm_s[i] = 0.f;
+    __syncthreads();
     float s[SSD_R];
 #pragma unroll
-    for (int i = 0; i < SSD_R; ++i) { const int n = ns + SSD_NS * i; s[i] = (n < N && live) ? S[(size_t)n * P + p] : 0.f; }
+    for (int i = 0; i < SSD_R; ++i) s[i] = (n0 + i < N && live) ? S[(size_t)(n0 + i) * P + p] : 0.f;
     const float negA = -__expf(a.A_log[h]), Dh = a.D[h], dtb = a.dt_bias[h];
     const int dtcol = 2 * inner + 2 * a.groups * N + h;
+    const int src_tok = SSD_COLS + 2 * N + 1;
+    // 16-byte copies when every segment starts on a 16-byte boundary (the usual geometry), 4-byte copies otherwise
+    const bool wide = ((N | P | inner | C | a.ldp | (a.groups * N)) & 3) == 0;
     auto fetch = [&](int c, float* dst) {                     // tokens [c * SSD_CH, ...) of the portion
         const int t0 = c * SSD_CH, nt = min(SSD_CH, len - t0);
-        for (int i = threadIdx.x; i < nt * per_tok; i += blockDim.x) {
-            const int t = i / per_tok, j = i - t * per_tok, r = r0 + t0 + t;
+        if (wide) {                                           // 8 threads per token: x (4 pieces), B and C (N / 4 pieces each), dt
+            const int t = threadIdx.x >> 3, q = threadIdx.x & 7, nq = N >> 2;
+            if (t < nt) {
+                const float* row = a.xbc + (size_t)(r0 + t0 + t) * C;
+                float* d0 = dst + t * per_tok;
+                for (int k = q; k < SSD_COLS / 4 + 2 * nq; k += 8) {
+                    if (k < SSD_COLS / 4) { if (4 * k < ncol) cp_async16s(d0 + 4 * k, row + h * P + p0 + 4 * k); }
+                    else if (k < SSD_COLS / 4 + nq) { const int n = 4 * (k - SSD_COLS / 4); cp_async16s(d0 + SSD_COLS + ssd_idx(n, SSD_R), row + inner + g * N + n); }
+                    else { const int n = 4 * (k - SSD_COLS / 4 - nq); cp_async16s(d0 + SSD_COLS + NP + ssd_idx(n, SSD_R), row + inner + (a.groups + g) * N + n); }
+                }
+                if (q == 0) cp_async4(d0 + SSD_COLS + 2 * NP, a.proj + (size_t)(r0 + t0 + t) * a.ldp + dtcol);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            return;
+        }
+        for (int i = threadIdx.x; i < nt * src_tok; i += blockDim.x) {
+            const int t = i / src_tok, j = i - t * src_tok, r = r0 + t0 + t;
             const float* src;
-            if (j < SSD_COLS) { if (j >= ncol) continue; src = a.xbc + (size_t)r * C + h * P + p0 + j; }
-            else if (j < SSD_COLS + N) src = a.xbc + (size_t)r * C + inner + g * N + (j - SSD_COLS);
-            else if (j < SSD_COLS + 2 * N) src = a.xbc + (size_t)r * C + inner + (a.groups + g) * N + (j - SSD_COLS - N);
-            else src = a.proj + (size_t)r * a.ldp + dtcol;
-            cp_async4(dst + i, src);
+            int d;
+            if (j < SSD_COLS) { if (j >= ncol) continue; src = a.xbc + (size_t)r * C + h * P + p0 + j; d = j; }
+            else if (j < SSD_COLS + N) { const int n = j - SSD_COLS; src = a.xbc + (size_t)r * C + inner + g * N + n; d = SSD_COLS + ssd_idx(n, SSD_R); }
+            else if (j < SSD_COLS + 2 * N) { const int n = j - SSD_COLS - N; src = a.xbc + (size_t)r * C + inner + (a.groups + g) * N + n; d = SSD_COLS + NP + ssd_idx(n, SSD_R); }
+            else { src = a.proj + (size_t)r * a.ldp + dtcol; d = SSD_COLS + 2 * NP; }
+            cp_async4(dst + t * per_tok + d, src);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -365,36 +435,39 @@ __global__ void __launch_bounds__(SSD_COLS * SSD_NS) ssd_scan_kernel(RaggedBatch
         __syncthreads();
         const float* st = stage[c & 1];
         const int nt = min(SSD_CH, len - c * SSD_CH);
-        if (threadIdx.x < nt) {
-            const float z = st[threadIdx.x * per_tok + SSD_COLS + 2 * N] + dtb;
-            const float dt = (z > 20.f) ? z : log1pf(__expf(z));
+        if (threadIdx.x < SSD_CH) {
+            const float z = st[threadIdx.x * per_tok + SSD_COLS + 2 * NP] + dtb;
+            const float dt = threadIdx.x < nt ? ((z > 20.f) ? z : log1pf(__expf(z))) : 0.f;      // past the end: the state stands still
             sdt[threadIdx.x] = dt; sdt[SSD_CH + threadIdx.x] = __expf(negA * dt);
         }
         __syncthreads();
-        for (int t = 0; t < nt; ++t) {
+        const int tmax = (nt + 3) & ~3;                       // whole groups of four: the padding tokens leave the state as it is
+#pragma unroll 4
+        for (int t = 0; t < tmax; ++t) {
             const float* tk = st + t * per_tok;
             const float dt = sdt[t], decay = sdt[SSD_CH + t];
             const float xv = live ? tk[pl] : 0.f;
-            const float* Br = tk + SSD_COLS;
-            const float* Cr = Br + N;
+            const float4* B4 = reinterpret_cast<const float4*>(tk + SSD_COLS + ssd_idx(n0, SSD_R));
+            const float4* C4 = reinterpret_cast<const float4*>(tk + SSD_COLS + NP + ssd_idx(n0, SSD_R));
             const float dx = dt * xv;
-            float y = 0.f;
+            float y0 = 0.f, y1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < SSD_R; ++i) {
-                const int n = ns + SSD_NS * i;
-                if (n < N) {
-                    s[i] = fmaf(decay, s[i], Br[n] * dx);
-                    y = fmaf(s[i], Cr[n], y);
-                }
+            for (int i = 0; i < SSD_R / 4; ++i) {
+                const float4 b = B4[i], cc = C4[i];
+                { s[4 * i]     = fmaf(decay, s[4 * i],     b.x * dx); y0 = fmaf(s[4 * i],     cc.x, y0); }
+                { s[4 * i + 1] = fmaf(decay, s[4 * i + 1], b.y * dx); y1 = fmaf(s[4 * i + 1], cc.y, y1); }
+                { s[4 * i + 2] = fmaf(decay, s[4 * i + 2], b.z * dx); y0 = fmaf(s[4 * i + 2], cc.z, y0); }
+                { s[4 * i + 3] = fmaf(decay, s[4 * i + 3], b.w * dx); y1 = fmaf(s[4 * i + 3], cc.w, y1); }
             }
+            float y = y0 + y1;
 #pragma unroll
             for (int o = SSD_NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (ns == 0 && live) a.y[(size_t)(r0 + c * SSD_CH + t) * inner + h * P + p] = y + Dh * xv;
+            if (ns == 0 && live && t < nt) a.y[(size_t)(r0 + c * SSD_CH + t) * inner + h * P + p] = y + Dh * xv;
         }
         __syncthreads();                                      // the stage is free for chunk c + 2
     }
 #pragma unroll
-    for (int i = 0; i < SSD_R; ++i) { const int n = ns + SSD_NS * i; if (n < N && live) S[(size_t)n * P + p] = s[i]; }
+    for (int i = 0; i < SSD_R; ++i) if (n0 + i < N && live) S[(size_t)(n0 + i) * P + p] = s[i];
 }
 
 // out = unit_rms_per_group(y * silu(z)) * w : block per (row, group)
@@ -434,6 +507,42 @@ __global__ void route_kernel(MoeArgs a) {
     for (int e = lane; e < a.E; e += 32) den += expf(z[e] - mx);
     den = warp_sum(den);
     unsigned long long taken[4] = {0, 0, 0, 0};         // E <= 256: bit per expert, same in every lane
+    for (int k = 0; k < a.top; ++k) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int e = lane; e < a.E; e += 32)
+            if (!((taken[e >> 6] >> (e & 63)) & 1ull) && (z[e] > bv)) { bv = z[e]; bi = e; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        taken[bi >> 6] |= 1ull << (bi & 63);
+        if (lane == 0) { a.sel_e[(size_t)r * a.top + k] = bi; a.sel_w[(size_t)r * a.top + k] = expf(bv - mx) / den; }
+    }
+}
+
+// Few rows (decode): router logits, softmax and top-k in one block per row.  Warp w computes the logits of experts w, w + 8, ...
+// (f32 products of the f32 row with the bf16 router rows, lanes striding the width), warp 0 then selects as route_kernel does.
+__global__ void __launch_bounds__(256) route_rows_kernel(MoeArgs a, const bf16* __restrict__ w_router, int ldw) {
+    __shared__ float z[256];
+    const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* h = a.h + (size_t)r * a.ldh;
+    for (int e = warp; e < a.E; e += 8) {
+        const bf16* wr = w_router + (size_t)e * ldw;
+        float acc = 0.f;
+        for (int k = lane; k < a.W; k += 32) acc = fmaf(h[k], __bfloat162float(wr[k]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) { z[e] = acc; a.router_logits[(size_t)r * a.ldr + e] = acc; }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float mx = -INFINITY;
+    for (int e = lane; e < a.E; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int e = lane; e < a.E; e += 32) den += expf(z[e] - mx);
+    den = warp_sum(den);
+    unsigned long long taken[4] = {0, 0, 0, 0};
     for (int k = 0; k < a.top; ++k) {
         float bv = -INFINITY; int bi = 0x7fffffff;
         for (int e = lane; e < a.E; e += 32)
@@ -652,32 +761,53 @@ int attn_prep_launch(cudaStream_t st, const RaggedBatch& rb, const AttnPrepArgs&
     else attn_prep_kernel<bf16><<<rb.T, 256, 0, st>>>(rb, a);
     return last_err();
 }
+template <typename KT, int REP>
+static int sink_attention_launch_t(cudaStream_t st, const RaggedBatch& rb, const SinkAttnArgs& a) {
+    const int rep = a.H / a.G, nb = (rep + REP - 1) / REP;
+    const size_t smem = (size_t)(REP * a.d + 2 * ATT_WARPS * REP + ATT_WARPS * REP * a.dv) * sizeof(float);
+    if (smem > 200 * 1024) return -1000;
+    static SmemOptIn seen;
+    if (const int e = ensure_dyn_smem(sink_attention_kernel<KT, REP>, smem, seen)) return e;
+    sink_attention_kernel<KT, REP><<<dim3(rb.T, a.G * nb, a.nsplit), ATT_WARPS * 32, smem, st>>>(rb, a);
+    return last_err();
+}
+template <typename KT>
+static int sink_attention_launch_k(cudaStream_t st, const RaggedBatch& rb, const SinkAttnArgs& a) {
+    const int rep = a.H / a.G;
+    // few blocks (a decode step): one query head per block keeps more SMs busy than sharing the keys would save
+    if (rep == 1 || (long long)rb.T * a.H * a.nsplit <= 1024) return sink_attention_launch_t<KT, 1>(st, rb, a);
+    if (rep == 2) return sink_attention_launch_t<KT, 2>(st, rb, a);
+    if (rep <= 4) return sink_attention_launch_t<KT, 4>(st, rb, a);
+    return sink_attention_launch_t<KT, 8>(st, rb, a);
+}
 int sink_attention_launch(cudaStream_t st, const RaggedBatch& rb, const SinkAttnArgs& a) {
     if (a.dv > 32 * ATT_MAXC || a.H % a.G) return -1000;
-    const size_t smem = (size_t)(a.d + 2 * ATT_WARPS + ATT_WARPS * a.dv) * sizeof(float);
-    const dim3 grid(rb.T, a.H, a.nsplit);
-    if (a.kv_f32) sink_attention_kernel<float><<<grid, ATT_WARPS * 32, smem, st>>>(rb, a);
-    else sink_attention_kernel<bf16><<<grid, ATT_WARPS * 32, smem, st>>>(rb, a);
-    int e = last_err();
+    int e = a.kv_f32 ? sink_attention_launch_k<float>(st, rb, a) : sink_attention_launch_k<bf16>(st, rb, a);
     if (e || a.nsplit == 1) return e;
     if (a.nsplit > 64) return -1000;
     sink_attention_merge_kernel<<<dim3(rb.T, a.H), 128, 0, st>>>(a);
     return last_err();
 }
-int mamba2_launch_count() { return 4; }
+int mamba2_launch_count(bool single_rows) { return single_rows ? 3 : 4; }
 int mamba2_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba2Args& a) {
     const int inner = a.heads * a.P, C = inner + 2 * a.groups * a.N;
     if (a.N > SSD_NS * SSD_MAXR || a.heads % a.groups || inner % a.norm_groups || a.taps < 1) return -1000;
-    conv_silu_kernel<<<dim3((C + 127) / 128, rb.T), 128, 0, st>>>(rb, a, C, inner);
-    int e = last_err();
-    if (e) return e;
-    if (a.taps > 1) {
-        conv_window_kernel<<<dim3((C + 127) / 128, rb.E), 128, 0, st>>>(rb, a, C, inner);
+    int e;
+    if (a.single_rows) {
+        conv_step_kernel<<<dim3((C + 127) / 128, rb.E), 128, 0, st>>>(rb, a, C, inner);
         if ((e = last_err())) return e;
+    } else {
+        conv_silu_kernel<<<dim3((C + 127) / 128, rb.T), 128, 0, st>>>(rb, a, C, inner);
+        if ((e = last_err())) return e;
+        if (a.taps > 1) {
+            conv_window_kernel<<<dim3((C + 127) / 128, rb.E), 128, 0, st>>>(rb, a, C, inner);
+            if ((e = last_err())) return e;
+        }
     }
     const dim3 sgrid(rb.E, a.heads, (a.P + SSD_COLS - 1) / SSD_COLS);
     const int nr = (a.N + SSD_NS - 1) / SSD_NS, sthreads = SSD_COLS * SSD_NS;
-    const size_t ssm = (size_t)(2 * SSD_CH * (SSD_COLS + 2 * a.N + 1) + 2 * SSD_CH) * sizeof(float);      // <= 67 KB at N = 256
+    const int rr = nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32;
+    const size_t ssm = (size_t)(2 * SSD_CH * (SSD_COLS + 2 * ssd_npad(a.N, rr) + 4) + 2 * SSD_CH) * sizeof(float);      // <= 78 KB at N = 256
     static SmemOptIn seen4, seen8, seen16, seen32;
     if (nr <= 4) { if ((e = ensure_dyn_smem(ssd_scan_kernel<4>, ssm, seen4))) return e; ssd_scan_kernel<4><<<sgrid, sthreads, ssm, st>>>(rb, a, C); }
     else if (nr <= 8) { if ((e = ensure_dyn_smem(ssd_scan_kernel<8>, ssm, seen8))) return e; ssd_scan_kernel<8><<<sgrid, sthreads, ssm, st>>>(rb, a, C); }
@@ -691,10 +821,17 @@ int clamped_glu_launch(cudaStream_t st, const float* gu, int ld, int up_off, int
     clamped_glu_kernel<<<dim3((F + 127) / 128, T), 128, 0, st>>>(gu, ld, up_off, F, limit, out);
     return last_err();
 }
-int moe_route_launch(cudaStream_t st, const MoeArgs& a) {
+int moe_route_launch(cudaStream_t st, const MoeArgs& a, const bf16* w_router, int ldw) {
     if (a.E > 256 || a.top > a.E || a.top < 1) return -1000;
-    route_kernel<<<(a.T + 3) / 4, 128, 0, st>>>(a);
-    int e = last_err();
+    int e;
+    if (a.T <= 64) {          // few rows: logits + selection in one launch
+        route_rows_kernel<<<a.T, 256, 0, st>>>(a, w_router, ldw);
+        e = last_err();
+    } else {
+        if ((e = linear_f32_launch(st, a.h, a.ldh, w_router, ldw, a.T, a.E, a.W, LIN_STORE, (float*)a.router_logits, a.ldr))) return e;
+        route_kernel<<<(a.T + 3) / 4, 128, 0, st>>>(a);
+        e = last_err();
+    }
     if (e) return e;
     moe_sort_kernel<<<1, 1024, (size_t)3 * a.E * sizeof(int), st>>>(a);
     return last_err();

@@ -75,9 +75,10 @@ struct Mamba2Args {
     float* xbc;                       // [T, C] scratch: conv + silu
     float* y;                         // [T, heads * P] scratch
     ActOut out;                       // gated, normalised [T, heads * P]
+    int single_rows = 0;              // every entry brings exactly one row (a decode step): convolution and window shift fuse
 };
 int mamba2_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba2Args& a);
-int mamba2_launch_count();
+int mamba2_launch_count(bool single_rows);
 
 // out[r, j] = g * sigmoid(1.702 g) * (u + 1),  g = min(gu[r, j], limit),  u = clamp(gu[r, up_off + j], -limit, limit)
 int clamped_glu_launch(cudaStream_t st, const float* gu, int ld, int up_off, int T, int F, float limit, const ActOut& out);
@@ -85,7 +86,7 @@ int clamped_glu_launch(cudaStream_t st, const float* gu, int ld, int up_off, int
 struct MoeArgs {
     int T, E, top, F, W;              // rows, experts, experts per row, expert width, model width
     const float* h; int ldh;          // [T, ldh] f32 input rows
-    const float* router_logits; int ldr;   // [T, ldr]
+    float* router_logits; int ldr;    // [T, ldr]
     const bf16* const* up;            // [E] device pointers, each [F, ldwu]
     const bf16* const* down;          // [E] each [W, ldwd]
     int ldwu, ldwd;
@@ -97,8 +98,8 @@ struct MoeArgs {
     float* y; int ldy;                // [T * top, ldy]
     float* x; int ldx;                // residual, += sum_k w_k y_k
 };
-// router softmax + top-k, then the counting sort by expert (2 launches)
-int moe_route_launch(cudaStream_t st, const MoeArgs& a);
+// router logits (f32 products: a.h x w_router^T -> a.router_logits), softmax + top-k, then the counting sort by expert
+int moe_route_launch(cudaStream_t st, const MoeArgs& a, const bf16* w_router, int ldw);
 // experts as grouped f32 linears over the sorted pairs + the ordered combine into x (3 launches): y rows indexed by pair
 int moe_experts_launch(cudaStream_t st, const MoeArgs& a);
 // tensor-core expert path: rows of `src` (bf16 planes) gathered into expert order, dense GEMMs per expert by the caller (y rows in
