@@ -194,7 +194,7 @@ gemv_kernel(GemvArgs a) {
             for (int b = 0; b < B; ++b) {
                 const float r = NORM ? rstd_s[b] : 1.f;
                 const float g = acc_s[(size_t)b * rpc + 2 * u] * r, up = acc_s[(size_t)b * rpc + 2 * u + 1] * r;
-                a.y[(size_t)b * a.ldy + (r0 / 2 + u)] = silu_f(g) * up;
+                a.y[(size_t)b * a.ldy + (r0 / 2 + u)] = glu_pair_f(g, up, a.glu_limit);
             }
         }
     } else {

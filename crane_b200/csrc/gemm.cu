@@ -95,7 +95,7 @@ __device__ __forceinline__ void epi_store32(const GemmEpi& ep, int m, int n, flo
         const size_t off = (size_t)m * ep.ldo + (n >> 1);
         uint32_t p[8], q[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) split_bf16x2(silu_f(v[4 * j]) * v[4 * j + 1], silu_f(v[4 * j + 2]) * v[4 * j + 3], p[j], q[j]);
+        for (int j = 0; j < 8; ++j) split_bf16x2(glu_pair_f(v[4 * j], v[4 * j + 1], ep.glu_limit), glu_pair_f(v[4 * j + 2], v[4 * j + 3], ep.glu_limit), p[j], q[j]);
         bf16* o = reinterpret_cast<bf16*>(ep.out) + off;
         *reinterpret_cast<uint4*>(o) = make_uint4(p[0], p[1], p[2], p[3]);
         *reinterpret_cast<uint4*>(o + 8) = make_uint4(p[4], p[5], p[6], p[7]);

@@ -20,7 +20,8 @@ enum GemmEpiMode : int {
     EPI_STORE_F32 = 0,     // out f32 [M, ldo] = acc (+ bias)
     EPI_STORE_BF16 = 1,    // out bf16 [M, ldo] = acc (+ bias)
     EPI_RESID_F32 = 2,     // out f32 [M, ldo] += acc (+ bias)           (residual stream, in place)
-    EPI_SILU_MUL_BF16 = 3, // W rows interleaved (gate_j, up_j): out bf16 [M, ldo][j] = silu(acc[2j]) * acc[2j+1]
+    EPI_SILU_MUL_BF16 = 3, // W rows interleaved (gate_j, up_j): out bf16 [M, ldo][j] = silu(acc[2j]) * acc[2j+1]; with GemmEpi::glu_limit > 0
+                           // the clamped unit instead: g = min(acc[2j], L), u = clamp(acc[2j+1], -L, L), out = g * sigmoid(1.702 g) * (u + 1)
     EPI_GELU_ERF_BF16 = 4, // out bf16 = gelu_erf(acc + bias)
     EPI_GELU_TANH_BF16 = 5 // out bf16 = gelu_tanh(acc + bias)
 };
@@ -32,6 +33,7 @@ struct GemmEpi {
     const float* bias;  // [N] or nullptr
     int mode;
     bool w_dynamic = false;   // W was written by an earlier kernel of the chain (dequantised scratch): no weight prefetch before the dependency wait
+    float glu_limit = 0.f;    // EPI_SILU_MUL_BF16 only: 0 = SiLU(gate) * up; > 0 = the clamped gated unit with this limit
     unsigned long long* prof = nullptr;   // optional: 8 globaltimer stamps per CTA (tile timeline, tools/gemm_probe.py)
 };
 

@@ -487,11 +487,11 @@ __global__ void gated_group_rms_kernel(Mamba2Args a) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------- feed-forwards
-__global__ void clamped_glu_kernel(const float* __restrict__ gu, int ld, int up_off, int F, float limit, ActOut out) {
+__global__ void clamped_glu_kernel(const float* __restrict__ gu, int ld, int stride, int up_off, int F, float limit, ActOut out) {
     const int r = blockIdx.y, j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= F) return;
-    const float g = fminf(gu[(size_t)r * ld + j], limit);
-    const float u = fminf(fmaxf(gu[(size_t)r * ld + up_off + j], -limit), limit);
+    const float g = fminf(gu[(size_t)r * ld + (size_t)j * stride], limit);
+    const float u = fminf(fmaxf(gu[(size_t)r * ld + (size_t)j * stride + up_off], -limit), limit);
     store_act(out, r, j, g / (1.f + __expf(-1.702f * g)) * (u + 1.f));
 }
 
@@ -817,8 +817,8 @@ int mamba2_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba2Args
     gated_group_rms_kernel<<<dim3(rb.T, a.norm_groups), 128, 0, st>>>(a);
     return last_err();
 }
-int clamped_glu_launch(cudaStream_t st, const float* gu, int ld, int up_off, int T, int F, float limit, const ActOut& out) {
-    clamped_glu_kernel<<<dim3((F + 127) / 128, T), 128, 0, st>>>(gu, ld, up_off, F, limit, out);
+int clamped_glu_launch(cudaStream_t st, const float* gu, int ld, int stride, int up_off, int T, int F, float limit, const ActOut& out) {
+    clamped_glu_kernel<<<dim3((F + 127) / 128, T), 128, 0, st>>>(gu, ld, stride, up_off, F, limit, out);
     return last_err();
 }
 int moe_route_launch(cudaStream_t st, const MoeArgs& a, const bf16* w_router, int ldw) {

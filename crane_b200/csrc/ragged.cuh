@@ -80,8 +80,9 @@ struct Mamba2Args {
 int mamba2_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba2Args& a);
 int mamba2_launch_count(bool single_rows);
 
-// out[r, j] = g * sigmoid(1.702 g) * (u + 1),  g = min(gu[r, j], limit),  u = clamp(gu[r, up_off + j], -limit, limit)
-int clamped_glu_launch(cudaStream_t st, const float* gu, int ld, int up_off, int T, int F, float limit, const ActOut& out);
+// out[r, j] = g * sigmoid(1.702 g) * (u + 1),  g = min(gu[r, js], limit),  u = clamp(gu[r, js + up_off], -limit, limit),  js = j * stride
+// (stride 2, up_off 1: interleaved (gate, up) pairs, the layout the fused GEMM / GEMV epilogues read)
+int clamped_glu_launch(cudaStream_t st, const float* gu, int ld, int stride, int up_off, int T, int F, float limit, const ActOut& out);
 
 struct MoeArgs {
     int T, E, top, F, W;              // rows, experts, experts per row, expert width, model width

@@ -401,3 +401,68 @@ def test_on_device_greedy_loop_equals_step_by_step():
     assert rel(lg[1], ref) < F32_TOL
     assert m.seq_len(s1) == 100 and m.kv_len() == 80
     m.close()
+
+
+# ---------------------------------------------------------------------------------------------------- CPU: the scheduler's bookkeeping
+class _FakeEngine:
+    """Stands in for a model handle: counts pages as the engine does and hands out token t + 1 for every wanted row."""
+
+    def __init__(self, max_tokens, max_batch):
+        self.config = {"engine": {"max_tokens": max_tokens, "max_batch": max_batch}}
+        self.pool, self.max_batch = max_tokens // 64, max_batch
+        self.len = {0: 0}
+        self.steps, self.last = [], []
+
+    def _pages(self):
+        return sum((n + 63) // 64 for n in self.len.values())
+
+    def seq_create(self):
+        s = min(i for i in range(self.max_batch) if i not in self.len)
+        self.len[s] = 0
+        return s
+
+    def seq_free(self, s):
+        del self.len[s]
+
+    def seq_select(self, s):
+        pass
+
+    def clear_kv_cache(self):
+        self.len[0] = 0
+
+    def step_batch(self, entries, copy=True):
+        assert len({e[0] for e in entries}) == len(entries) <= self.max_batch
+        for s, toks, want in entries:
+            assert s in self.len and len(toks) > 0
+            self.len[s] += len(toks)
+        assert self._pages() <= self.pool
+        self.steps.append([(s, len(t), list(w)) for s, t, w in entries])
+        self.last = [t[w_] + 1 for s, t, w in entries for w_ in w]
+
+    def sample_rows(self, params):
+        assert len(params) == len(self.last)
+        return np.asarray(self.last, np.uint32)
+
+
+def test_scheduler_admission_chunking_and_page_accounting():
+    from crane_b200.scheduler import BatchScheduler
+    eng = _FakeEngine(max_tokens=512, max_batch=3)                     # 8 pages, 3 slots
+    sch = BatchScheduler(eng, chunk=50, max_live=3, token_budget=70)
+    prompts = [[10] * 130, [20] * 60, [30] * 200, [40] * 5]
+    rids = [sch.add(p, 4) for p in prompts]
+    out = sch.run()
+    # every request got its tokens: the fake feeds back last + 1, so a prompt of value v yields v + 1, v + 2, ...
+    for rid, p in zip(rids, prompts):
+        assert out[rid] == [p[0] + 1 + i for i in range(4)]
+    for st in eng.steps:
+        assert sum(n for _, n, _ in st) <= 70                          # the token budget holds in every iteration
+        assert all(n <= 50 for _, n, _ in st)
+    # prompt portions and single decoded tokens do share iterations
+    assert any(any(n > 1 for _, n, _ in st) and any(n == 1 for _, n, _ in st) for st in eng.steps)
+    assert eng.len == {0: 0}                                           # every slot but the handle's own is free again, pages returned
+    with pytest.raises(ValueError):
+        BatchScheduler(eng).add([], 3)
+    big = BatchScheduler(eng, chunk=64)
+    big.add([1] * 600, 8)                                              # larger than the whole pool
+    with pytest.raises(ValueError):
+        big.run()
