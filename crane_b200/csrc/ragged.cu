@@ -189,17 +189,25 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
         if (j < nkeys) {
             const KT* kr = (const KT*)a.k_pool + (base + lane) * d;
             if (kvec) {
-                for (int c = 0; c < d; c += 8) {
-                    float kf[8];
-                    kv_load8<KT>(kr + c, a.kv_lo_off, kf);
+                // UN pieces of the key row are requested before the first is used: the loop is bound by memory latency, not by arithmetic
+                constexpr int UN = REP <= 2 ? 4 : 2;
+                for (int c0 = 0; c0 < d; c0 += 8 * UN) {
+                    float kf[UN][8];
 #pragma unroll
-                    for (int q = 0; q < REP; ++q) {
-                        if (q < nh) {
-                            const float4 qa = *reinterpret_cast<const float4*>(sq + q * d + c), qb = *reinterpret_cast<const float4*>(sq + q * d + c + 4);
-                            float x = sc[q];
-                            x = fmaf(qa.x, kf[0], x); x = fmaf(qa.y, kf[1], x); x = fmaf(qa.z, kf[2], x); x = fmaf(qa.w, kf[3], x);
-                            x = fmaf(qb.x, kf[4], x); x = fmaf(qb.y, kf[5], x); x = fmaf(qb.z, kf[6], x); x = fmaf(qb.w, kf[7], x);
-                            sc[q] = x;
+                    for (int u = 0; u < UN; ++u) if (c0 + 8 * u < d) kv_load8<KT>(kr + c0 + 8 * u, a.kv_lo_off, kf[u]);
+#pragma unroll
+                    for (int u = 0; u < UN; ++u) {
+                        const int c = c0 + 8 * u;
+                        if (c >= d) break;
+#pragma unroll
+                        for (int q = 0; q < REP; ++q) {
+                            if (q < nh) {
+                                const float4 qa = *reinterpret_cast<const float4*>(sq + q * d + c), qb = *reinterpret_cast<const float4*>(sq + q * d + c + 4);
+                                float x = sc[q];
+                                x = fmaf(qa.x, kf[u][0], x); x = fmaf(qa.y, kf[u][1], x); x = fmaf(qa.z, kf[u][2], x); x = fmaf(qa.w, kf[u][3], x);
+                                x = fmaf(qb.x, kf[u][4], x); x = fmaf(qb.y, kf[u][5], x); x = fmaf(qb.z, kf[u][6], x); x = fmaf(qb.w, kf[u][7], x);
+                                sc[q] = x;
+                            }
                         }
                     }
                 }
@@ -227,15 +235,22 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
         const KT* vb = (const KT*)a.v_pool + base * dv;
         if (vvec) {
             const bool mine = 8 * lane < dv;
-            for (int jj = 0; jj < cnt; ++jj) {
-                float v[8];
-                if (mine) kv_load8<KT>(vb + (size_t)jj * dv + 8 * lane, a.kv_lo_off, v);
+            constexpr int VN = REP <= 2 ? 4 : 2;              // value rows in flight
+            for (int j0 = 0; j0 < cnt; j0 += VN) {
+                float v[VN][8];
 #pragma unroll
-                for (int q = 0; q < REP; ++q) {
-                    const float pj = __shfl_sync(0xffffffffu, p[q], jj);
-                    if (mine && q < nh) {
+                for (int u = 0; u < VN; ++u) if (mine && j0 + u < cnt) kv_load8<KT>(vb + (size_t)(j0 + u) * dv + 8 * lane, a.kv_lo_off, v[u]);
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) acc[q][c] = fmaf(pj, v[c], acc[q][c]);
+                for (int u = 0; u < VN; ++u) {
+                    const int jj = j0 + u;                    // (uniform over the warp)
+                    if (jj >= cnt) break;
+#pragma unroll
+                    for (int q = 0; q < REP; ++q) {
+                        const float pj = __shfl_sync(0xffffffffu, p[q], jj);
+                        if (mine && q < nh) {
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) acc[q][c] = fmaf(pj, v[u][c], acc[q][c]);
+                        }
                     }
                 }
             }

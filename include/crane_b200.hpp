@@ -106,6 +106,24 @@ class B200Backend : public ModelBackend {
         return out;
     }
 
+    // ---- ragged-batch step of a layer-list model: entries = (sequence, its next tokens, wanted positions); logits stay on the device ----
+    struct StepEntry { int seq; std::vector<uint32_t> tokens; std::vector<uint32_t> want; };
+    crane_b200_logits step_batch(const std::vector<StepEntry>& entries) {
+        std::vector<crane_b200_step_entry> es(entries.size());
+        for (size_t i = 0; i < entries.size(); ++i)
+            es[i] = crane_b200_step_entry{entries[i].seq, entries[i].tokens.data(), entries[i].tokens.size(),
+                                          entries[i].want.empty() ? nullptr : entries[i].want.data(), entries[i].want.size()};
+        crane_b200_logits lg{};
+        ck(crane_b200_step_batch(h_, es.data(), es.size(), &lg));
+        return lg;
+    }
+    std::vector<uint32_t> sample_rows(const std::vector<crane_b200_sampling>& params) {
+        std::vector<uint32_t> out(params.size());
+        ck(crane_b200_sample_rows(h_, params.data(), params.size(), out.data()));
+        return out;
+    }
+    size_t seq_len(int s) const { size_t n = 0; crane_b200_seq_len(h_, s, &n); return n; }
+
     // ---- prefix sharing and the legacy tensor swap (backend.rs:65-84 get_kv_caches / set_kv_caches) ----
     int seq_fork(int src) { int s = -1; ck(crane_b200_seq_fork(h_, src, &s)); return s; }
     struct LayerCache { std::vector<float> k, v; size_t n_tokens = 0; };      // attention layer: [n_kv, T, D] each

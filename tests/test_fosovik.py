@@ -370,8 +370,12 @@ def test_tensor_core_attention_and_expert_gemms(precision, tol):
     s1 = m.seq_create()
     got = m.step_batch([(0, a[300:], all_rows(100)), (s1, b[:149], all_rows(149))])   # cached prefix + a second sequence, ragged
     assert rel(got[:100], wa[300:]) < tol and rel(got[100:], wb[:149]) < tol
-    got = m.step_batch([(s1, b[149:], [0])])
-    assert rel(got, wb[149:]) < tol
+    # a single decoded token of one sequence (399 cached keys) beside a fresh 40-row prompt: still the many-row kernels
+    c = tokens(40, WIDE["vocab"], 64)
+    wc = o.forward(c, o.new_state()).numpy()
+    s2 = m.seq_create()
+    got = m.step_batch([(s1, b[149:], [0]), (s2, c, all_rows(40))])
+    assert rel(got[:1], wb[149:]) < tol and rel(got[1:], wc) < tol
     m.close()
 
 
