@@ -470,3 +470,102 @@ def test_scheduler_admission_chunking_and_page_accounting():
     big.add([1] * 600, 8)                                              # larger than the whole pool
     with pytest.raises(ValueError):
         big.run()
+
+
+# ---------------------------------------------------------------------------------------------------- random geometries
+def random_config(seed):
+    """A layer list drawn at random: widths that are and are not multiples of 8, every grouping of query heads, shared keys / values,
+    one to five taps, layers without a feed-forward, experts with top-1 .. top-all."""
+    r = np.random.default_rng(1000 + seed)
+    pick = lambda *xs: xs[int(r.integers(len(xs)))]
+    width, vocab = int(pick(72, 96, 136, 200, 264)), int(pick(61, 150, 257, 512))
+    layers, att_at = [], []
+    for i in range(int(r.integers(3, 7))):
+        if r.random() < 0.5:
+            G = int(pick(1, 2, 3)); rep = int(pick(1, 2, 3, 4, 6, 8))
+            m = {"heads": G * rep, "kv_heads": G, "dim": int(pick(8, 12, 16, 24, 40, 64)), "vdim": int(pick(8, 10, 16, 24, 48)),
+                 "scale": float(pick(0.2, 0.5, 1.0))}
+            if r.random() < 0.6:
+                m["q_temp"] = {"coef": float(pick(0.1, 0.5, 1.0)), "every": int(pick(1, 7, 32, 100))}
+            same = [j for j in att_at if layers[j]["mixer"].get("kv_from") is None]
+            if same and r.random() < 0.4:
+                src = layers[int(pick(*same))]["mixer"]
+                m.update(kv_heads=src["kv_heads"], dim=src["dim"], vdim=src["vdim"], heads=src["kv_heads"] * rep,
+                         kv_from=int(next(j for j in same if layers[j]["mixer"] is src)))
+            L = {"type": "attention", "mixer": m}
+            att_at.append(i)
+        else:
+            groups = int(pick(1, 2, 3)); hp = int(pick(1, 2, 4))
+            P = int(pick(4, 12, 16, 20, 40))
+            ng = int(pick(1, 2, groups * hp))
+            while (groups * hp * P) % ng:
+                ng -= 1
+            L = {"type": "mamba2", "mixer": {"heads": groups * hp, "vdim": P, "state": int(pick(4, 8, 16, 33, 64)), "groups": groups,
+                                             "conv": int(pick(1, 2, 3, 4, 5)), "norm_groups": ng}}
+        k = r.random()
+        if k < 0.2:
+            L["mlp"] = None
+        elif k < 0.55:
+            L["mlp"] = {"kind": "dense", "ff": int(pick(24, 100, 256, 300)), "limit": float(pick(0.5, 2.0, 7.0))}
+        else:
+            E = int(pick(2, 3, 8, 11))
+            L["mlp"] = {"kind": "moe", "expert": {"ff": int(pick(8, 36, 64))}, "router": {"experts": E, "top": int(r.integers(1, E + 1))}}
+        layers.append(L)
+    return {"architecture": "Fosovik", "vocab": vocab, "width": width, "embedding": {"scale": float(pick(1.0, 4.0, 11.0))},
+            "norm": {"eps": float(pick(1e-6, 1e-5, 1e-3))}, "layers": layers}
+
+
+def test_random_configs_are_valid_for_the_oracle():
+    for seed in range(10):
+        cfg = random_config(seed)
+        o = FosovikOracle(cfg, random_weights(cfg, seed))
+        ids = tokens(9, cfg["vocab"], seed)
+        st = o.new_state()
+        a = o.forward(ids, o.new_state()).numpy()
+        b = np.concatenate([o.forward(ids[:4], st).numpy(), o.forward(ids[4:], st).numpy()])
+        assert np.isfinite(a).all() and rel(b, a) < 1e-10
+
+
+def rows_close(got, want, tol, cfg):
+    """Exact mode: every row within tol.  Serving precision: operand rounding may flip a router choice that was nearly a tie, which
+    moves that row by O(1) in either implementation -- a model with experts may have a few such rows, all others must hold the bar."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    err = np.abs(got - want).max(-1) / np.abs(want).max()
+    has_experts = any((L.get("mlp") or {}).get("kind") == "moe" for L in cfg["layers"])
+    if tol <= F32_TOL or not has_experts:
+        return bool((err < tol).all())
+    return float((err < tol).mean()) >= 0.9
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("precision,tol", [("f32", F32_TOL), ("split", SPLIT_TOL)])
+@pytest.mark.parametrize("seed", range(10))
+def test_random_geometries_whole_chunked_and_mixed(seed, precision, tol):
+    cfg = random_config(seed)
+    m, o = make(cfg, seed, precision=precision, max_tokens=768, max_batch=3)
+    r = np.random.default_rng(seed)
+    pa, pb, pc = (tokens(int(n), cfg["vocab"], 100 * seed + i) for i, n in enumerate((r.integers(70, 200), r.integers(2, 90), r.integers(65, 140))))
+    wa, wb, wc = (o.forward(p, o.new_state()).numpy() for p in (pa, pb, pc))
+    assert rows_close(m.step_batch([(0, pa, all_rows(len(pa)))]), wa, tol, cfg)               # whole
+    s1, s2 = m.seq_create(), m.seq_create()
+    at, got = {s1: 0, s2: 0}, {s1: [], s2: []}
+    src = {s1: pb, s2: pc}
+    while any(at[s] < len(src[s]) for s in src):                                              # random cuts, both sequences side by side
+        entries = []
+        for s in src:
+            left = len(src[s]) - at[s]
+            if left and r.random() < 0.8:
+                n = int(min(left, r.choice([1, 1, 2, 3, 17, 40, 64])))
+                entries.append((s, src[s][at[s]:at[s] + n], all_rows(n)))
+        if not entries:
+            continue
+        lg = m.step_batch(entries)
+        k = 0
+        for s, t, w in entries:
+            got[s].append(lg[k:k + len(t)]); k += len(t); at[s] += len(t)
+    assert rows_close(np.concatenate(got[s1]), wb, tol, cfg) and rows_close(np.concatenate(got[s2]), wc, tol, cfg)
+    m.seq_free(s1)
+    m.clear_kv_cache()                                                                        # pages and slots again, with one token at a time
+    rows = np.concatenate([m.step_batch([(0, [t], [0])]) for t in pb[:20]])
+    assert rows_close(rows, wb[:min(20, len(pb))], tol, cfg)
+    m.close()
