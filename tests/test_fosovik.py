@@ -569,3 +569,45 @@ def test_random_geometries_whole_chunked_and_mixed(seed, precision, tol):
     rows = np.concatenate([m.step_batch([(0, [t], [0])]) for t in pb[:20]])
     assert rows_close(rows, wb[:min(20, len(pb))], tol, cfg)
     m.close()
+
+
+# ---------------------------------------------------------------------------------------------------- the ends of the supported ranges
+@pytest.mark.gpu
+@pytest.mark.parametrize("precision,tol", [("f32", F32_TOL), ("split", SPLIT_TOL)])
+def test_widest_heads_largest_state_many_experts(precision, tol):
+    att = {"type": "attention", "mixer": {"heads": 6, "kv_heads": 1, "dim": 256, "vdim": 256, "scale": 0.3, "q_temp": {"coef": 0.2, "every": 50}}}
+    ssm = {"type": "mamba2", "mixer": {"heads": 2, "vdim": 136, "state": 256, "groups": 2, "conv": 4, "norm_groups": 1}}
+    ssm2 = {"type": "mamba2", "mixer": {"heads": 3, "vdim": 8, "state": 130, "groups": 1, "conv": 3, "norm_groups": 3}}
+    moe = {"kind": "moe", "expert": {"ff": 24}, "router": {"experts": 70, "top": 5}}
+    cfg = config([dict(att, mlp=dict(DENSE)), dict(ssm, mlp=None), dict(ssm2, mlp=moe if precision == "f32" else dict(DENSE)),
+                  layer(att, None, kv_from=0)], width=192, vocab=333)
+    m, o = make(cfg, 81, precision=precision, max_tokens=512, max_batch=2)
+    a, b = tokens(200, cfg["vocab"], 82), tokens(90, cfg["vocab"], 83)
+    wa, wb = o.forward(a, o.new_state()).numpy(), o.forward(b, o.new_state()).numpy()
+    s1 = m.seq_create()
+    got = m.step_batch([(0, a[:150], all_rows(150)), (s1, b[:30], all_rows(30))])
+    assert rel(got[:150], wa[:150]) < tol and rel(got[150:], wb[:30]) < tol
+    got = m.step_batch([(0, a[150:151], [0]), (s1, b[30:], all_rows(60))])               # one decoded token beside a 60-row portion
+    assert rel(got[:1], wa[150:151]) < tol and rel(got[1:], wb[30:]) < tol
+    rows = np.concatenate([m.step_batch([(0, [t], [0])]) for t in a[151:160]])
+    assert rel(rows, wa[151:160]) < tol
+    m.close()
+
+
+@pytest.mark.gpu
+def test_step_batch_rejects_bad_requests_and_stays_usable():
+    import crane_b200
+    m, o = make(SINGLE["dense"], 91, precision="f32", max_tokens=128, max_batch=2)
+    V = SINGLE["dense"]["vocab"]
+    ids = tokens(10, V, 92)
+    for bad in ([(0, ids, [10])],                       # wanted position past the portion
+                [(0, [V], [0])],                        # token outside the vocabulary
+                [(0, ids, [0]), (0, ids, [0])],         # the same sequence twice
+                [(1, ids, [0])],                        # a slot nobody created
+                [(0, [], [])],                          # nothing to run
+                [(0, tokens(200, V, 93), [])]):         # more pages than the pool has
+        with pytest.raises(crane_b200.CraneB200Error):
+            m.step_batch(bad)
+    assert m.seq_len(0) == 0
+    assert rel(m.step_batch([(0, ids, all_rows(10))]), o.forward(ids, o.new_state()).numpy()) < F32_TOL
+    m.close()
