@@ -388,26 +388,39 @@ __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
 // all banks.
 __host__ __device__ inline int ssd_idx(int n, int R) { return n + 4 * (n / R); }
 __host__ __device__ inline int ssd_npad(int N, int R) { (void)N; return 8 * (R + 4); }      // all eight runs, whatever N: no bounds checks in the loop
-template <int SSD_R>                                         // state rows per thread: ceil(N / 8) rounded up to 4, 8, 16 or 32
+// Long portions are cut into SSD_SEGS segments that run side by side (the scan has one resident warp per scheduler and waits on
+// its own dependent chain most of the time): the recurrence is linear with a SCALAR decay per head and token, so
+//   S_end(segment) = (product of the segment's decays) * S_start + S_local(segment run from zero).
+// MODE 1 runs every segment from zero and leaves S_local and the decay product; ssd_seg_prefix_kernel turns them into each segment's
+// start state (and the sequence's new state); MODE 2 is the scan proper from those start states.  MODE 0 = one segment, everything.
+constexpr int SSD_SEGS = 4, SSD_SEG_MIN = 512;              // segmented from this many rows in the longest entry
+__host__ __device__ inline int ssd_seg_len(int len) { return ((len + SSD_SEGS - 1) / SSD_SEGS + SSD_CH - 1) / SSD_CH * SSD_CH; }
+template <int SSD_R, int MODE>                               // state rows per thread: ceil(N / 8) rounded up to 4, 8, 16 or 32
 __global__ void __launch_bounds__(SSD_COLS * SSD_NS) ssd_scan_kernel(RaggedBatch rb, Mamba2Args a, int C) {
     extern __shared__ __align__(16) float ssm_s[];
-    const int e = blockIdx.x, h = blockIdx.y, ns = threadIdx.x & (SSD_NS - 1), pl = threadIdx.x / SSD_NS;
+    const int e = MODE == 0 ? blockIdx.x : blockIdx.x / SSD_SEGS, seg = MODE == 0 ? 0 : blockIdx.x % SSD_SEGS;
+    const int h = blockIdx.y, ns = threadIdx.x & (SSD_NS - 1), pl = threadIdx.x / SSD_NS;
     const int p0 = blockIdx.z * SSD_COLS, p = p0 + pl;
     const int P = a.P, N = a.N, inner = a.heads * P, g = h / (a.heads / a.groups);
     const bool live = p < P;
-    const int len = rb.ent_len[e], r0 = rb.ent_row0[e], slot = rb.ent_slot[e];
+    const int full_len = rb.ent_len[e], slot = rb.ent_slot[e];
+    const int seg_len = MODE == 0 ? full_len : ssd_seg_len(full_len), seg0 = seg * seg_len;
+    if (seg0 >= full_len) return;                             // (a short entry has fewer segments)
+    const int len = min(seg_len, full_len - seg0), r0 = rb.ent_row0[e] + seg0;
     const int ncol = min(SSD_COLS, P - p0);
     const int NP = ssd_npad(N, SSD_R), per_tok = SSD_COLS + 2 * NP + 4;
     float* stage[2] = {ssm_s, ssm_s + SSD_CH * per_tok};
     float* sdt = ssm_s + 2 * SSD_CH * per_tok;                // [SSD_CH] dt, [SSD_CH] decay
-    float* S = a.ssm_state + (((size_t)slot * a.heads + h) * N) * P;
+    float* S = MODE == 0 ? a.ssm_state + (((size_t)slot * a.heads + h) * N) * P
+                         : a.seg_state + ((((size_t)e * SSD_SEGS + seg) * a.heads + h) * N) * P;
     const int n0 = ns * SSD_R;
     // rows past N and tokens past the portion's end multiply zeros: the stages start zeroed and only real values are ever copied in
     for (int i = threadIdx.x; i < 2 * SSD_CH * per_tok; i += blockDim.x) ssm_s[i] = 0.f;
     __syncthreads();
     float s[SSD_R];
 #pragma unroll
-    for (int i = 0; i < SSD_R; ++i) s[i] = (n0 + i < N && live) ? S[(size_t)(n0 + i) * P + p] : 0.f;
+    for (int i = 0; i < SSD_R; ++i) s[i] = (MODE != 1 && n0 + i < N && live) ? S[(size_t)(n0 + i) * P + p] : 0.f;
+    float dprod = 1.f;                                        // MODE 1, thread 0: product of the segment's decays
     const float negA = -__expf(a.A_log[h]), Dh = a.D[h], dtb = a.dt_bias[h];
     const int dtcol = 2 * inner + 2 * a.groups * N + h;
     const int src_tok = SSD_COLS + 2 * N + 1;
@@ -456,6 +469,7 @@ __global__ void __launch_bounds__(SSD_COLS * SSD_NS) ssd_scan_kernel(RaggedBatch
             sdt[threadIdx.x] = dt; sdt[SSD_CH + threadIdx.x] = __expf(negA * dt);
         }
         __syncthreads();
+        if (MODE == 1 && threadIdx.x == 0) for (int t = 0; t < nt; ++t) dprod *= sdt[SSD_CH + t];
         const int tmax = (nt + 3) & ~3;                       // whole groups of four: the padding tokens leave the state as it is
 #pragma unroll 4
         for (int t = 0; t < tmax; ++t) {
@@ -465,6 +479,15 @@ __global__ void __launch_bounds__(SSD_COLS * SSD_NS) ssd_scan_kernel(RaggedBatch
             const float4* B4 = reinterpret_cast<const float4*>(tk + SSD_COLS + ssd_idx(n0, SSD_R));
             const float4* C4 = reinterpret_cast<const float4*>(tk + SSD_COLS + NP + ssd_idx(n0, SSD_R));
             const float dx = dt * xv;
+            if (MODE == 1) {                                  // state only
+#pragma unroll
+                for (int i = 0; i < SSD_R / 4; ++i) {
+                    const float4 b = B4[i];
+                    s[4 * i] = fmaf(decay, s[4 * i], b.x * dx); s[4 * i + 1] = fmaf(decay, s[4 * i + 1], b.y * dx);
+                    s[4 * i + 2] = fmaf(decay, s[4 * i + 2], b.z * dx); s[4 * i + 3] = fmaf(decay, s[4 * i + 3], b.w * dx);
+                }
+                continue;
+            }
             float y0 = 0.f, y1 = 0.f;
 #pragma unroll
             for (int i = 0; i < SSD_R / 4; ++i) {
@@ -481,8 +504,26 @@ __global__ void __launch_bounds__(SSD_COLS * SSD_NS) ssd_scan_kernel(RaggedBatch
         }
         __syncthreads();                                      // the stage is free for chunk c + 2
     }
+    if (MODE == 2) return;                                    // the prefix kernel already wrote the sequence's new state
 #pragma unroll
     for (int i = 0; i < SSD_R; ++i) if (n0 + i < N && live) S[(size_t)(n0 + i) * P + p] = s[i];
+    if (MODE == 1 && threadIdx.x == 0 && blockIdx.z == 0) a.seg_decay[((size_t)e * SSD_SEGS + seg) * a.heads + h] = dprod;
+}
+// Start state of every segment, in order: seg_state[k] holds S_local on entry and S_start(k) on exit; the slot gets the end state.
+__global__ void ssd_seg_prefix_kernel(RaggedBatch rb, Mamba2Args a) {
+    const int e = blockIdx.x, h = blockIdx.y, np = a.N * a.P;
+    const int len = rb.ent_len[e], slot = rb.ent_slot[e], nseg = (len + ssd_seg_len(len) - 1) / ssd_seg_len(len);
+    float* S = a.ssm_state + ((size_t)slot * a.heads + h) * np;
+    for (int i = blockIdx.z * blockDim.x + threadIdx.x; i < np; i += gridDim.z * blockDim.x) {
+        float cur = S[i];
+        for (int k = 0; k < nseg; ++k) {
+            float* loc = a.seg_state + (((size_t)e * SSD_SEGS + k) * a.heads + h) * np + i;
+            const float l = *loc;
+            *loc = cur;
+            cur = fmaf(a.seg_decay[((size_t)e * SSD_SEGS + k) * a.heads + h], cur, l);
+        }
+        S[i] = cur;
+    }
 }
 
 // out = unit_rms_per_group(y * silu(z)) * w : block per (row, group)
@@ -803,7 +844,8 @@ int sink_attention_launch(cudaStream_t st, const RaggedBatch& rb, const SinkAttn
     sink_attention_merge_kernel<<<dim3(rb.T, a.H), 128, 0, st>>>(a);
     return last_err();
 }
-int mamba2_launch_count(bool single_rows) { return single_rows ? 3 : 4; }
+int mamba2_launch_count(bool single_rows, int max_len) { return single_rows ? 3 : max_len >= SSD_SEG_MIN ? 6 : 4; }
+size_t mamba2_seg_floats(int entries, int heads, int N, int P) { return (size_t)entries * SSD_SEGS * heads * ((size_t)N * P + 1); }
 int mamba2_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba2Args& a) {
     const int inner = a.heads * a.P, C = inner + 2 * a.groups * a.N;
     if (a.N > SSD_NS * SSD_MAXR || a.heads % a.groups || inner % a.norm_groups || a.taps < 1) return -1000;
@@ -823,11 +865,25 @@ int mamba2_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba2Args
     const int nr = (a.N + SSD_NS - 1) / SSD_NS, sthreads = SSD_COLS * SSD_NS;
     const int rr = nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32;
     const size_t ssm = (size_t)(2 * SSD_CH * (SSD_COLS + 2 * ssd_npad(a.N, rr) + 4) + 2 * SSD_CH) * sizeof(float);      // <= 78 KB at N = 256
-    static SmemOptIn seen4, seen8, seen16, seen32;
-    if (nr <= 4) { if ((e = ensure_dyn_smem(ssd_scan_kernel<4>, ssm, seen4))) return e; ssd_scan_kernel<4><<<sgrid, sthreads, ssm, st>>>(rb, a, C); }
-    else if (nr <= 8) { if ((e = ensure_dyn_smem(ssd_scan_kernel<8>, ssm, seen8))) return e; ssd_scan_kernel<8><<<sgrid, sthreads, ssm, st>>>(rb, a, C); }
-    else if (nr <= 16) { if ((e = ensure_dyn_smem(ssd_scan_kernel<16>, ssm, seen16))) return e; ssd_scan_kernel<16><<<sgrid, sthreads, ssm, st>>>(rb, a, C); }
-    else { if ((e = ensure_dyn_smem(ssd_scan_kernel<32>, ssm, seen32))) return e; ssd_scan_kernel<32><<<sgrid, sthreads, ssm, st>>>(rb, a, C); }
+    const bool segs = a.seg_state != nullptr && a.max_len >= SSD_SEG_MIN;
+    auto run = [&](auto kern, SmemOptIn& seen, dim3 grid) -> int {
+        if (const int er = ensure_dyn_smem(kern, ssm, seen)) return er;
+        kern<<<grid, sthreads, ssm, st>>>(rb, a, C);
+        return last_err();
+    };
+    auto scan = [&](auto k4, auto k8, auto k16, auto k32, SmemOptIn* seen, dim3 grid) -> int {
+        return nr <= 4 ? run(k4, seen[0], grid) : nr <= 8 ? run(k8, seen[1], grid) : nr <= 16 ? run(k16, seen[2], grid) : run(k32, seen[3], grid);
+    };
+    static SmemOptIn seen0[4], seen1[4], seen2[4];
+    if (!segs) {
+        if ((e = scan(ssd_scan_kernel<4, 0>, ssd_scan_kernel<8, 0>, ssd_scan_kernel<16, 0>, ssd_scan_kernel<32, 0>, seen0, sgrid))) return e;
+    } else {
+        const dim3 ggrid(rb.E * SSD_SEGS, a.heads, sgrid.z);
+        if ((e = scan(ssd_scan_kernel<4, 1>, ssd_scan_kernel<8, 1>, ssd_scan_kernel<16, 1>, ssd_scan_kernel<32, 1>, seen1, ggrid))) return e;
+        ssd_seg_prefix_kernel<<<dim3(rb.E, a.heads, 8), 256, 0, st>>>(rb, a);
+        if ((e = last_err())) return e;
+        if ((e = scan(ssd_scan_kernel<4, 2>, ssd_scan_kernel<8, 2>, ssd_scan_kernel<16, 2>, ssd_scan_kernel<32, 2>, seen2, ggrid))) return e;
+    }
     if ((e = last_err())) return e;
     gated_group_rms_kernel<<<dim3(rb.T, a.norm_groups), 128, 0, st>>>(a);
     return last_err();

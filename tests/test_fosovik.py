@@ -611,3 +611,22 @@ def test_step_batch_rejects_bad_requests_and_stays_usable():
     assert m.seq_len(0) == 0
     assert rel(m.step_batch([(0, ids, all_rows(10))]), o.forward(ids, o.new_state()).numpy()) < F32_TOL
     m.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("precision,tol", [("f32", F32_TOL), ("split", SPLIT_TOL)])
+def test_long_portions_scan_in_segments(precision, tol):
+    """From 512 rows in the longest entry the Mamba-2 scan runs as four segments joined by their decay products: a long entry on a
+    carried state, a short one beside it (one segment), then more rows on the states both left."""
+    cfg = config([layer(SSM, DENSE), layer(SSM1), layer(ATT_PLAIN)], width=96, vocab=211)
+    m, o = make(cfg, 95, precision=precision, max_tokens=1536, max_batch=2)
+    a, b = tokens(900, cfg["vocab"], 96), tokens(120, cfg["vocab"], 97)
+    wa, wb = o.forward(a, o.new_state()).numpy(), o.forward(b, o.new_state()).numpy()
+    s1 = m.seq_create()
+    m.step_batch([(0, a[:37], [])])                                                  # a state to start from
+    want = [36, 37, 300, 511, 512, 700]
+    got = m.step_batch([(0, a[37:740], [w - 37 for w in want[1:]]), (s1, b[:5], [4])])      # 703 rows: segments of 176
+    assert rel(got[:-1], wa[want[1:]]) < tol and rel(got[-1:], wb[4:5]) < tol
+    got = m.step_batch([(s1, b[5:], [114]), (0, a[740:], [0, 159])])                 # short portions again: one segment
+    assert rel(got[:1], wb[119:]) < tol and rel(got[1:], wa[[740, 899]]) < tol
+    m.close()
