@@ -109,6 +109,15 @@ gemv_kernel(GemvArgs a) {
                 lo.x *= w0.x; lo.y *= w0.y; lo.z *= w0.z; lo.w *= w0.w;
                 hi.x *= w1.x; hi.y *= w1.y; hi.z *= w1.z; hi.w *= w1.w;
             }
+            if (!NORM && a.dyt_w != nullptr) {
+                const float al = *a.dyt_alpha;
+                const float4 w0 = reinterpret_cast<const float4*>(a.dyt_w)[2 * i], w1 = reinterpret_cast<const float4*>(a.dyt_w)[2 * i + 1];
+                const float4 b0 = reinterpret_cast<const float4*>(a.dyt_b)[2 * i], b1 = reinterpret_cast<const float4*>(a.dyt_b)[2 * i + 1];
+                lo.x = fmaf(tanhf(al * lo.x), w0.x, b0.x); lo.y = fmaf(tanhf(al * lo.y), w0.y, b0.y);
+                lo.z = fmaf(tanhf(al * lo.z), w0.z, b0.z); lo.w = fmaf(tanhf(al * lo.w), w0.w, b0.w);
+                hi.x = fmaf(tanhf(al * hi.x), w1.x, b1.x); hi.y = fmaf(tanhf(al * hi.y), w1.y, b1.y);
+                hi.z = fmaf(tanhf(al * hi.z), w1.z, b1.z); hi.w = fmaf(tanhf(al * hi.w), w1.w, b1.w);
+            }
             xs[(size_t)(b * 2 + 0) * K8 + i] = lo;
             xs[(size_t)(b * 2 + 1) * K8 + i] = hi;
         }

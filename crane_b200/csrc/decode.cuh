@@ -55,6 +55,9 @@ struct GemvArgs {
     int advance;            // 0: report the argmax only; 1: feed it back (token, next embedding, kv_len/pos + 1);
                             // 2: advance kv_len/pos and gather embed[state.token] WITHOUT replacing the token (caller-chosen input)
     float* norm_out;        // optional [B, K]: the RMS-normalised input (x * w * rstd), written by CTA 0 (NORM kernels)
+    // kernels without the RMSNorm fold: a Dynamic-Tanh norm applied while x is staged, x <- tanh(alpha x) * w + b (w, b hold K
+    // entries, zeros behind the model width); nullptr = x as it is
+    const float* dyt_alpha; const float* dyt_w; const float* dyt_b;
     float glu_limit;        // GEMV_SILU_MUL: 0 = SiLU(gate) * up; > 0 = the clamped gated unit with this limit (common.cuh glu_pair_f)
     const uint32_t* force_tokens;  // optional [out_stride]: teacher forcing -- token fed back at step s is force_tokens[s] (argmax still reported)
 };

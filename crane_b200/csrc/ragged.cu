@@ -846,6 +846,7 @@ int sink_attention_launch(cudaStream_t st, const RaggedBatch& rb, const SinkAttn
 }
 int mamba2_launch_count(bool single_rows, int max_len) { return single_rows ? 3 : max_len >= SSD_SEG_MIN ? 6 : 4; }
 size_t mamba2_seg_floats(int entries, int heads, int N, int P) { return (size_t)entries * SSD_SEGS * heads * ((size_t)N * P + 1); }
+size_t mamba2_seg_decay_offset(int entries, int heads, int N, int P) { return (size_t)entries * SSD_SEGS * heads * (size_t)N * P; }
 int mamba2_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba2Args& a) {
     const int inner = a.heads * a.P, C = inner + 2 * a.groups * a.N;
     if (a.N > SSD_NS * SSD_MAXR || a.heads % a.groups || inner % a.norm_groups || a.taps < 1) return -1000;

@@ -76,7 +76,7 @@ struct Mamba2Args {
     float* y;                         // [T, heads * P] scratch
     ActOut out;                       // gated, normalised [T, heads * P]
     int single_rows = 0;              // every entry brings exactly one row (a decode step): convolution and window shift fuse
-    // long portions run as four segments side by side (see ssd_scan_kernel): scratch for their local / start states and decay
+    // long portions run as segments side by side (see ssd_scan_kernel): scratch for their local / start states and decay
     // products, mamba2_seg_floats(entries, ...) floats in all; nullptr = never segment
     float* seg_state = nullptr; float* seg_decay = nullptr;
     int max_len = 0;                  // rows of the longest entry
@@ -84,6 +84,7 @@ struct Mamba2Args {
 int mamba2_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba2Args& a);
 int mamba2_launch_count(bool single_rows, int max_len);
 size_t mamba2_seg_floats(int entries, int heads, int N, int P);
+size_t mamba2_seg_decay_offset(int entries, int heads, int N, int P);
 
 // out[r, j] = g * sigmoid(1.702 g) * (u + 1),  g = min(gu[r, js], limit),  u = clamp(gu[r, js + up_off], -limit, limit),  js = j * stride
 // (stride 2, up_off 1: interleaved (gate, up) pairs, the layout the fused GEMM / GEMV epilogues read)
