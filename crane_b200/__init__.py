@@ -627,10 +627,20 @@ class FosovikModel(Qwen3Model):
     Engine options: max_tokens (page pool), max_batch (sequence slots), precision ("split", "bf16", "f32")."""
 
 
+class GavipelModel(FosovikModel):
+    """A layer-list decoder ("architecture": "Gavipel"): per layer two RMS norms feeding sliding-window attention (weighted QK norm,
+    pairwise rotation of the leading dimensions, zero-score sink, sigmoid output gate) and a mixture of SiLU-gated experts (sigmoid
+    scores, selection bias, group-limited choice, one expert for every token), each branch scaled per column; a span of the layer
+    list may repeat with pages of its own per pass; the head is the embedding table.  Same entry points and engine options as
+    `FosovikModel`."""
+
+
 # config.json -> model class, as `model_factory::create_backend` picks a backend by architecture (crane-serve/src/engine/model_factory.rs:471-560)
 def model_class(config: dict):
     if config.get("architecture") == "Fosovik":
         return FosovikModel
+    if config.get("architecture") == "Gavipel":
+        return GavipelModel
     if "talker_config" in config:
         return Qwen3TTSModel
     if "vision_config" in config:

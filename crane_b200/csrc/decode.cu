@@ -123,7 +123,7 @@ gemv_kernel(GemvArgs a) {
         }
         if (NORM) {
             const float tot = block_sum(ssq, red);
-            if (tid == 0) rstd_s[b] = rsqrtf(tot / (float)a.K + a.eps);
+            if (tid == 0) rstd_s[b] = rsqrtf(tot / (float)(a.norm_dim > 0 ? a.norm_dim : a.K) + a.eps);
         }
     }
     __syncthreads();
@@ -212,7 +212,7 @@ gemv_kernel(GemvArgs a) {
             for (int b = 0; b < B; ++b) {
                 const float v = acc_s[(size_t)b * rpc + i] * (NORM ? rstd_s[b] : 1.f);
                 float* yp = a.y + (size_t)b * a.ldy + r0 + i;
-                if constexpr (EPI == GEMV_RESID) *yp += v; else *yp = v;
+                if constexpr (EPI == GEMV_RESID) *yp += a.out_scale ? a.out_scale[r0 + i] * v : v; else *yp = v;
                 if constexpr (EPI == GEMV_LOGITS_ARGMAX) {
                     if (v > bestv[b]) { bestv[b] = v; besti[b] = r0 + i; }   // a thread's rows ascend: first maximum wins
                 }

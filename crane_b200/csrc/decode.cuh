@@ -59,6 +59,8 @@ struct GemvArgs {
     // entries, zeros behind the model width); nullptr = x as it is
     const float* dyt_alpha; const float* dyt_w; const float* dyt_b;
     float glu_limit;        // GEMV_SILU_MUL: 0 = SiLU(gate) * up; > 0 = the clamped gated unit with this limit (common.cuh glu_pair_f)
+    int norm_dim;           // NORM kernels: the mean of squares divides by this many columns (0: K) -- a K padded with zero columns
+    const float* out_scale; // GEMV_RESID, nullable [N]: y[n] += out_scale[n] * (W x)[n]
     const uint32_t* force_tokens;  // optional [out_stride]: teacher forcing -- token fed back at step s is force_tokens[s] (argmax still reported)
 };
 

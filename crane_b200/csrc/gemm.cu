@@ -136,6 +136,13 @@ __device__ __forceinline__ void epi_block(const GemmEpi& ep, uint8_t* stg, int m
             v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
         }
     }
+    if (ep.col_scale != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const float4 c = *reinterpret_cast<const float4*>(ep.col_scale + n + j);
+            v[j] *= c.x; v[j + 1] *= c.y; v[j + 2] *= c.z; v[j + 3] *= c.w;
+        }
+    }
     if constexpr (MODE == EPI_STORE_F32 || MODE == EPI_RESID_F32) {
         uint8_t* mine = stg + lane * EPI_PITCH;
         // the residual rows first (independent loads, all in flight together), then the transpose
@@ -456,6 +463,8 @@ gemm_simt_kernel(const bf16* __restrict__ A, const bf16* __restrict__ A_lo, int 
     if (m < M && n0 < N) {
         if (ep.bias != nullptr)
             for (int j = 0; j < 32; ++j) acc[j] += ep.bias[n0 + j];
+        if (ep.col_scale != nullptr)
+            for (int j = 0; j < 32; ++j) acc[j] *= ep.col_scale[n0 + j];
         epi_store32<MODE>(ep, m, n0, acc, true);
     }
 }

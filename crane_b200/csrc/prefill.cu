@@ -260,6 +260,8 @@ flash_prefill_kernel(FlashArgs a) {
     const int* btab = (PAGED && a.seq_slot) ? a.block_table + (size_t)a.seq_slot[z] * a.bt_stride : a.block_table;
     const int kvh = head / (a.nh / a.nkv);
     const int n_tiles = CAUSAL ? min((T + BN - 1) / BN, (kv_off + q0 + BM - 1) / BN + 1) : (T + BN - 1) / BN;
+    // sliding window: the first query row of the tile is the one that reaches furthest back
+    const int t_first = (CAUSAL && a.window > 0) ? max(0, kv_off + q0 - a.window + 1) / BN : 0;
 
     // ---- Q tile -> smem (zero-fill rows past S) ----
     for (int c = tid; c < BM * CPR; c += 256) {
@@ -307,10 +309,10 @@ flash_prefill_kernel(FlashArgs a) {
     uint32_t qf[SPLIT ? 1 : D / 16][4];        // plain mode keeps the Q fragments in registers; SPLIT re-reads them from smem
 
     bool first = true;
-    if (grp < n_tiles) load_kv(grp, 0);
+    if (t_first + grp < n_tiles) load_kv(t_first + grp, 0);
     cp_async_commit();
     int it = 0;
-    for (int tile = grp; tile < n_tiles; tile += 2, ++it) {
+    for (int tile = t_first + grp; tile < n_tiles; tile += 2, ++it) {
         const int stage = STG == 2 ? (it & 1) : 0;
         if (STG == 2) {
             if (tile + 2 < n_tiles) load_kv(tile + 2, stage ^ 1);
@@ -384,7 +386,7 @@ flash_prefill_kernel(FlashArgs a) {
             for (int e = 0; e < 4; ++e) {
                 const int col = kv0 + j * 8 + tq * 2 + (e & 1);
                 const int qrow = q0 + warp * 16 + g + (e >> 1) * 8;
-                const bool vis = (col < T) && (!CAUSAL || col <= kv_off + qrow);
+                const bool vis = (col < T) && (!CAUSAL || (col <= kv_off + qrow && (a.window <= 0 || kv_off + qrow - col < a.window)));
                 const float v = vis ? s_acc[j][e] * sl2 : -INFINITY;
                 s_acc[j][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -494,10 +496,16 @@ flash_prefill_kernel(FlashArgs a) {
                 inv = c / (l_row[r] * c + exp2f(s2 - mn));
             }
             bf16* o = a.out + (size_t)(row0 + qrow) * a.o_stride + head * D;
+            const float* gt = a.gate ? a.gate + (size_t)(row0 + qrow) * a.g_stride + head * D : nullptr;
 #pragma unroll
             for (int i = 0; i < D / 8; ++i) {
                 uint32_t hi, lo;
-                split_bf16x2(o_acc[i][2 * r] * inv, o_acc[i][2 * r + 1] * inv, hi, lo);
+                float o0 = o_acc[i][2 * r] * inv, o1 = o_acc[i][2 * r + 1] * inv;
+                if (gt) {        // sigmoid output gate, in f32
+                    const float2 gv = *reinterpret_cast<const float2*>(gt + i * 8 + tq * 2);
+                    o0 *= 1.f / (1.f + __expf(-gv.x)); o1 *= 1.f / (1.f + __expf(-gv.y));
+                }
+                split_bf16x2(o0, o1, hi, lo);
                 *reinterpret_cast<uint32_t*>(o + i * 8 + tq * 2) = hi;
                 if (SPLIT) *reinterpret_cast<uint32_t*>(o + a.out_lo_off + i * 8 + tq * 2) = lo;
             }
@@ -521,6 +529,7 @@ static int flash_launch_t(cudaStream_t st, const FlashArgs& a) {
 int flash_prefill_launch(cudaStream_t st, int D, bool causal, bool paged, const FlashArgs& a) {
     const bool split = a.q_lo_off != 0;
     if (split && (a.kv_lo_off == 0 || a.out_lo_off == 0)) return -1000;
+    if (D == 64 && causal && paged) return split ? flash_launch_t<64, true, true, true>(st, a) : flash_launch_t<64, true, true, false>(st, a);
     if (D == 128 && causal && paged) return split ? flash_launch_t<128, true, true, true>(st, a) : flash_launch_t<128, true, true, false>(st, a);
     if (D == 256 && causal && paged) return split ? flash_launch_t<256, true, true, true>(st, a) : flash_launch_t<256, true, true, false>(st, a);
     if (D == 64 && !causal && !paged) return split ? flash_launch_t<64, false, false, true>(st, a) : flash_launch_t<64, false, false, false>(st, a);

@@ -57,6 +57,9 @@ struct FlashArgs {
     const int* seq_slot = nullptr;
     int bt_stride = 0;
     const float* sink = nullptr;        // [nh]: one extra term exp(sink_h) in every row's softmax denominator (no key, no value, unscaled)
+    int window = 0;                     // causal mode, > 0: query i sees keys j with 0 <= i - j < window (key tiles before the window are skipped)
+    const float* gate = nullptr;        // [rows, g_stride] f32, head h at h * D: out *= sigmoid(gate) before the store
+    int g_stride = 0;
 };
 
 // quantised KV pages <-> the bf16 (hi + lo) scratch the prefill kernels read and write (see prefill.cu)

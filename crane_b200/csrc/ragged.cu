@@ -53,6 +53,34 @@ __global__ void dyt_rows_kernel(const float* __restrict__ x, int ldx, const int*
     for (int c = threadIdx.x; c < W; c += blockDim.x) store_act(out, r, c, tanhf(a * x[(size_t)src * ldx + c]) * w[c] + b[c]);
 }
 
+// RMS norm of a row with up to two weight vectors on the one statistic.  The sum of squares runs in a fixed order (thread-strided
+// partial sums, then a tree over the block), so a row's result does not depend on what else is in the step.
+__global__ void __launch_bounds__(256) rms_rows_kernel(const float* __restrict__ x, int ldx, const int* __restrict__ rows, int W, float eps,
+                                                       const float* __restrict__ w1, ActOut out1, const float* __restrict__ w2, ActOut out2) {
+    __shared__ float red[8];
+    const int r = blockIdx.x, src = rows ? rows[r] : r, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* xr = x + (size_t)src * ldx;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += 256) ss = fmaf(xr[c], xr[c], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    const float inv = 1.f / sqrtf(tot / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += 256) {
+        const float v = xr[c] * inv;
+        store_act(out1, r, c, v * w1[c]);
+        if (w2) store_act(out2, r, c, v * w2[c]);
+    }
+}
+
+__global__ void store_rows_kernel(const float* __restrict__ src, int lds, int W, ActOut dst, int col0) {
+    const int r = blockIdx.x;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) store_act(dst, r, col0 + c, src[(size_t)r * lds + c]);
+}
+
 __global__ void gather_rows_kernel(const float* __restrict__ src, int lds, const int* __restrict__ rows, int W, float* __restrict__ dst, int ldd) {
     const int r = blockIdx.x;
     for (int c = threadIdx.x; c < W; c += blockDim.x) dst[(size_t)r * ldd + c] = src[(size_t)rows[r] * lds + c];
@@ -62,7 +90,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ src, int lds, const
 // 64 x 64 output tile, 16-wide k-steps, 256 threads x (4 x 4) accumulators; each output element sums k = 0 .. K-1 in order.
 template <int MODE>
 __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict__ A, int lda, const bf16* __restrict__ Wt, int ldw, int M, int N,
-                                                         int K, float* __restrict__ C, int ldc) {
+                                                         int K, float* __restrict__ C, int ldc, const float* __restrict__ col_scale) {
     __shared__ float sa[16][64 + 4], sw[16][64 + 4];
     const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64, tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     float acc[4][4] = {};
@@ -92,36 +120,61 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict
             const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
             if (m < M && n < N) {
                 float* p = C + (size_t)m * ldc + n;
-                *p = (MODE == LIN_RESID) ? *p + acc[i][j] : acc[i][j];
+                *p = (MODE == LIN_RESID) ? *p + (col_scale ? col_scale[n] * acc[i][j] : acc[i][j]) : acc[i][j];
             }
         }
 }
 
 // ---------------------------------------------------------------------------------------------------------------- attention
-// One warp per (row, head): q -> q / rms(q) * temp(pos); k -> k / rms(k) into its page; v into its page.
+// One warp per (row, head): q -> rms_norm(q) [* w] * temp(pos), rotated; k -> rms_norm(k) [* w], rotated, into its page; v into its page.
+// The rotation turns neighbouring pairs (2i, 2i + 1) of the first rot_dims dimensions by pos * rot_freq[i]; the row's cosines and
+// sines are taken once per row, in 64-bit, and shared by its heads.
 template <typename KT>
 __global__ void attn_prep_kernel(RaggedBatch rb, AttnPrepArgs a) {
+    extern __shared__ float rot_cs[];                    // [rot_dims / 2] cos, then sin
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int e = rb.row_entry[r], pos = rb.row_pos[r], slot = rb.ent_slot[e];
     const float* row = a.qkv + (size_t)r * a.ld;
     const int nheads = a.H + (a.has_kv ? 2 * a.G : 0);
+    const int nrot = a.rot_dims / 2;
+    if (nrot > 0) {
+        for (int i = threadIdx.x; i < nrot; i += blockDim.x) {
+            double sn, cs;
+            sincos((double)pos * a.rot_freq[i], &sn, &cs);
+            rot_cs[i] = (float)cs; rot_cs[nrot + i] = (float)sn;
+        }
+        __syncthreads();
+    }
     float temp = 1.f;
     if (a.temp_every > 0) temp = 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every) + 1.f);
     const int page = a.has_kv ? a.block_table[(size_t)slot * a.max_pages + pos / KV_PAGE] : 0;
     for (int hh = warp; hh < nheads; hh += nw) {
-        if (hh < a.H + a.G) {            // q or k head: unit RMS over d
+        if (hh < a.H + a.G) {            // q or k head: RMS norm over d
             const bool isq = hh < a.H;
             const float* src = row + (size_t)hh * a.d;
+            const float* nwt = isq ? a.q_norm_w : a.k_norm_w;
             float ss = 0.f;
             for (int c = lane; c < a.d; c += 32) ss += src[c] * src[c];
             ss = warp_sum(ss);
             const float inv = 1.f / sqrtf(ss / (float)a.d + a.eps) * (isq ? temp : 1.f);
-            if (isq) {
-                for (int c = lane; c < a.d; c += 32) store_act(a.q_out, r, hh * a.d + c, src[c] * inv);
-            } else {
-                const int g = hh - a.H;
-                KT* dst = (KT*)a.k_pool + (((size_t)page * a.G + g) * KV_PAGE + (pos % KV_PAGE)) * a.d;
-                for (int c = lane; c < a.d; c += 32) kv_store<KT>(dst + c, src[c] * inv, a.kv_lo_off);
+            KT* dst = nullptr;
+            if (!isq) dst = (KT*)a.k_pool + (((size_t)page * a.G + (hh - a.H)) * KV_PAGE + (pos % KV_PAGE)) * a.d;
+            // a lane owns the pairs (2i, 2i + 1), i = lane, lane + 32, ...: both halves of a rotated pair are in one thread
+            for (int c = 2 * lane; c < a.d; c += 64) {
+                float u = src[c] * inv, v = (c + 1 < a.d) ? src[c + 1] * inv : 0.f;
+                if (nwt) { u *= nwt[c]; if (c + 1 < a.d) v *= nwt[c + 1]; }
+                if (c + 1 < a.rot_dims) {
+                    const float cs = rot_cs[c >> 1], sn = rot_cs[nrot + (c >> 1)];
+                    const float u2 = u * cs - v * sn, v2 = v * cs + u * sn;
+                    u = u2; v = v2;
+                }
+                if (isq) {
+                    store_act(a.q_out, r, hh * a.d + c, u);
+                    if (c + 1 < a.d) store_act(a.q_out, r, hh * a.d + c + 1, v);
+                } else {
+                    kv_store<KT>(dst + c, u, a.kv_lo_off);
+                    if (c + 1 < a.d) kv_store<KT>(dst + c + 1, v, a.kv_lo_off);
+                }
             }
         } else {
             const int g = hh - a.H - a.G;
@@ -169,8 +222,10 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
     for (int i = threadIdx.x; i < nh * d; i += blockDim.x) sq[i] = a.q[(size_t)r * a.ldq + (size_t)h0 * d + i] * a.scale;
     __syncthreads();
     const int nkeys = pos + 1;
-    const int ntiles = (nkeys + 31) / 32, per = (ntiles + a.nsplit - 1) / a.nsplit;
-    const int t_lo = sp * per, t_hi = min(ntiles, t_lo + per);
+    const int key0 = (a.window > 0 && nkeys > a.window) ? nkeys - a.window : 0;      // first key the row sees
+    const int t0 = key0 / 32;                            // (its tile holds at least that key: no tile is hidden entirely)
+    const int ntiles = (nkeys + 31) / 32, per = (ntiles - t0 + a.nsplit - 1) / a.nsplit;
+    const int t_lo = t0 + sp * per, t_hi = min(ntiles, t_lo + per);
     float m[REP], l[REP], acc[REP][ATT_MAXC];
 #pragma unroll
     for (int q = 0; q < REP; ++q) {
@@ -186,7 +241,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
         float sc[REP];
 #pragma unroll
         for (int q = 0; q < REP; ++q) sc[q] = 0.f;
-        if (j < nkeys) {
+        const bool seen = j < nkeys && j >= key0;
+        if (seen) {
             const KT* kr = (const KT*)a.k_pool + (base + lane) * d;
             if (kvec) {
                 // UN pieces of the key row are requested before the first is used: the loop is bound by memory latency, not by arithmetic
@@ -222,10 +278,10 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
         float p[REP];
 #pragma unroll
         for (int q = 0; q < REP; ++q) {
-            const float sv = (j < nkeys) ? sc[q] : -INFINITY;
+            const float sv = seen ? sc[q] : -INFINITY;
             const float mn = fmaxf(m[q], warp_max(sv));
             const float corr = (m[q] == -INFINITY) ? 0.f : __expf(m[q] - mn);
-            p[q] = (j < nkeys) ? __expf(sv - mn) : 0.f;
+            p[q] = seen ? __expf(sv - mn) : 0.f;
             l[q] = l[q] * corr + warp_sum(p[q]);
 #pragma unroll
             for (int c = 0; c < ATT_MAXC; ++c) acc[q][c] *= corr;
@@ -291,7 +347,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
         for (int col = threadIdx.x; col < dv; col += blockDim.x) {
             float o = 0.f;
             for (int w = 0; w < ATT_WARPS; ++w) o += wa[((size_t)w * REP + q) * dv + col] * wsc[w];
-            if (last) store_act(a.out, r, h * dv + col, o / Lsum);
+            if (last) store_act(a.out, r, h * dv + col, o / Lsum * (a.gate ? 1.f / (1.f + __expf(-a.gate[(size_t)r * a.ldg + h * dv + col])) : 1.f));
             else a.part[(((size_t)r * a.H + h) * a.nsplit + sp) * (dv + 2) + 2 + col] = o;
         }
         if (!last && threadIdx.x == 0) {
@@ -323,7 +379,7 @@ __global__ void sink_attention_merge_kernel(SinkAttnArgs a) {
         float o = 0.f;
 #pragma unroll 4
         for (int sp = 0; sp < ns; ++sp) o = fmaf(pp[(size_t)sp * (dv + 2) + 2 + col], wgt[sp], o);
-        store_act(a.out, r, h * dv + col, o * invL);
+        store_act(a.out, r, h * dv + col, o * invL * (a.gate ? 1.f / (1.f + __expf(-a.gate[(size_t)r * a.ldg + h * dv + col])) : 1.f));
     }
 }
 
@@ -551,36 +607,87 @@ __global__ void clamped_glu_kernel(const float* __restrict__ gu, int ld, int str
     store_act(out, r, j, g / (1.f + __expf(-1.702f * g)) * (u + 1.f));
 }
 
-// softmax over all experts, the `top` largest (ties: lowest index), weights = the scores themselves.  One warp per row.
-__global__ void route_kernel(MoeArgs a) {
-    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (r >= a.T) return;
-    const float* z = a.router_logits + (size_t)r * a.ldr;
-    float mx = -INFINITY;
-    for (int e = lane; e < a.E; e += 32) mx = fmaxf(mx, z[e]);
-    mx = warp_max(mx);
-    float den = 0.f;
-    for (int e = lane; e < a.E; e += 32) den += expf(z[e] - mx);
-    den = warp_sum(den);
+__global__ void silu_glu_kernel(const float* __restrict__ gu, int ld, int F, ActOut out) {
+    const int r = blockIdx.y, j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= F) return;
+    store_act(out, r, j, silu_f(gu[(size_t)r * ld + 2 * j]) * gu[(size_t)r * ld + 2 * j + 1]);
+}
+
+// Expert choice for one row by one warp.  z: the row's router logits; sc / ch / gs: 256 floats each of this warp's scratch.
+// Scores = softmax over all experts or element-wise sigmoid; the choice value adds the selection bias; with n_groups > 1 only the
+// experts of the `keep` groups with the largest (sum of the two largest choice values) stay eligible -- the others count as
+// minus infinity; the `top` largest choice values win (ties: lowest index) and carry the plain scores as weights.
+__device__ __forceinline__ void choose_experts(const MoeArgs& a, const float* z, int r, int lane, float* sc, float* ch, float* gs) {
+    const int E = a.E;
+    if (a.score_fn == 1) {
+        for (int e = lane; e < E; e += 32) sc[e] = 1.f / (1.f + expf(-z[e]));
+    } else {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        float den = 0.f;
+        for (int e = lane; e < E; e += 32) den += expf(z[e] - mx);
+        den = warp_sum(den);
+        for (int e = lane; e < E; e += 32) sc[e] = expf(z[e] - mx) / den;
+    }
+    for (int e = lane; e < E; e += 32) ch[e] = sc[e] + (a.correction ? a.correction[e] : 0.f);
+    __syncwarp();
+    if (a.n_groups > 1) {
+        const int per = E / a.n_groups;
+        for (int g = lane; g < a.n_groups; g += 32) {
+            float b0 = -INFINITY, b1 = -INFINITY;
+            for (int i = 0; i < per; ++i) { const float v = ch[g * per + i]; if (v > b0) { b1 = b0; b0 = v; } else if (v > b1) b1 = v; }
+            gs[g] = per > 1 ? b0 + b1 : b0;
+        }
+        __syncwarp();
+        unsigned long long kept[4] = {0, 0, 0, 0};
+        for (int k = 0; k < a.keep; ++k) {
+            float bv = -INFINITY; int bi = 0x7fffffff;
+            for (int g = lane; g < a.n_groups; g += 32)
+                if (!((kept[g >> 6] >> (g & 63)) & 1ull) && gs[g] > bv) { bv = gs[g]; bi = g; }
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            if (bi == 0x7fffffff)                        // (no comparable value left: the lowest group not kept yet)
+                for (int g = 0; g < a.n_groups; ++g) if (!((kept[g >> 6] >> (g & 63)) & 1ull)) { bi = g; break; }
+            kept[bi >> 6] |= 1ull << (bi & 63);
+        }
+        for (int e = lane; e < E; e += 32) { const int g = e / per; if (!((kept[g >> 6] >> (g & 63)) & 1ull)) ch[e] = -INFINITY; }
+        __syncwarp();
+    }
     unsigned long long taken[4] = {0, 0, 0, 0};         // E <= 256: bit per expert, same in every lane
     for (int k = 0; k < a.top; ++k) {
         float bv = -INFINITY; int bi = 0x7fffffff;
-        for (int e = lane; e < a.E; e += 32)
-            if (!((taken[e >> 6] >> (e & 63)) & 1ull) && (z[e] > bv)) { bv = z[e]; bi = e; }
+        for (int e = lane; e < E; e += 32)
+            if (!((taken[e >> 6] >> (e & 63)) & 1ull) && (ch[e] > bv)) { bv = ch[e]; bi = e; }
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
+        if (bi == 0x7fffffff) {                          // nothing eligible is left (every value minus infinity or NaN): lowest free index, weight 0
+            for (int e = 0; e < E; ++e) if (!((taken[e >> 6] >> (e & 63)) & 1ull)) { bi = e; break; }
+            if (lane == 0) { a.sel_e[(size_t)r * a.top + k] = bi; a.sel_w[(size_t)r * a.top + k] = 0.f; }
+        } else if (lane == 0) { a.sel_e[(size_t)r * a.top + k] = bi; a.sel_w[(size_t)r * a.top + k] = sc[bi]; }
         taken[bi >> 6] |= 1ull << (bi & 63);
-        if (lane == 0) { a.sel_e[(size_t)r * a.top + k] = bi; a.sel_w[(size_t)r * a.top + k] = expf(bv - mx) / den; }
     }
 }
 
-// Few rows (decode): router logits, softmax and top-k in one block per row.  Warp w computes the logits of experts w, w + 8, ...
+// One warp per row, logits from global memory.
+__global__ void __launch_bounds__(128) route_kernel(MoeArgs a) {
+    __shared__ float scr[4][3][256];
+    const int warp = threadIdx.x >> 5, r = blockIdx.x * 4 + warp, lane = threadIdx.x & 31;
+    if (r >= a.T) return;
+    choose_experts(a, a.router_logits + (size_t)r * a.ldr, r, lane, scr[warp][0], scr[warp][1], scr[warp][2]);
+}
+
+// Few rows (decode): router logits and the choice in one block per row.  Warp w computes the logits of experts w, w + 8, ...
 // (f32 products of the f32 row with the bf16 router rows, lanes striding the width), warp 0 then selects as route_kernel does.
 __global__ void __launch_bounds__(256) route_rows_kernel(MoeArgs a, const bf16* __restrict__ w_router, int ldw) {
     __shared__ float z[256];
+    __shared__ float scr[3][256];
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* h = a.h + (size_t)r * a.ldh;
     for (int e = warp; e < a.E; e += 8) {
@@ -592,25 +699,7 @@ __global__ void __launch_bounds__(256) route_rows_kernel(MoeArgs a, const bf16* 
     }
     __syncthreads();
     if (warp != 0) return;
-    float mx = -INFINITY;
-    for (int e = lane; e < a.E; e += 32) mx = fmaxf(mx, z[e]);
-    mx = warp_max(mx);
-    float den = 0.f;
-    for (int e = lane; e < a.E; e += 32) den += expf(z[e] - mx);
-    den = warp_sum(den);
-    unsigned long long taken[4] = {0, 0, 0, 0};
-    for (int k = 0; k < a.top; ++k) {
-        float bv = -INFINITY; int bi = 0x7fffffff;
-        for (int e = lane; e < a.E; e += 32)
-            if (!((taken[e >> 6] >> (e & 63)) & 1ull) && (z[e] > bv)) { bv = z[e]; bi = e; }
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-        }
-        taken[bi >> 6] |= 1ull << (bi & 63);
-        if (lane == 0) { a.sel_e[(size_t)r * a.top + k] = bi; a.sel_w[(size_t)r * a.top + k] = expf(bv - mx) / den; }
-    }
+    choose_experts(a, z, r, lane, scr[0], scr[1], scr[2]);
 }
 
 // Counting sort of the (row, choice) pairs by expert + the tile map of the grouped linears (32 pairs per tile).  One block.
@@ -648,7 +737,7 @@ __global__ void __launch_bounds__(256) moe_linear_kernel(MoeArgs a) {
     const int tile = blockIdx.y;
     if (tile >= *a.n_tiles) return;
     const int e = a.tile_e[tile], r0 = a.tile_r0[tile], nr = a.tile_n[tile];
-    const int N = UP ? a.F : a.W, K = UP ? a.W : a.F, ldw = UP ? a.ldwu : a.ldwd;
+    const int N = UP ? (a.gated ? 2 * a.F : a.F) : a.W, K = UP ? a.W : a.F, ldw = UP ? a.ldwu : a.ldwd;
     const bf16* Wt = UP ? a.up[e] : a.down[e];
     const int n0 = blockIdx.x * 64, tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;      // thread: 2 pairs x 4 columns
     if (tid < 32) spair[tid] = tid < nr ? a.sorted[r0 + tid] : -1;
@@ -682,8 +771,10 @@ __global__ void __launch_bounds__(256) moe_linear_kernel(MoeArgs a) {
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
-            if (UP) a.act[(size_t)pr * a.lda + n] = gelu_erf_f(acc[i][j]);
-            else a.y[(size_t)pr * a.ldy + n] = acc[i][j];
+            if (UP) {
+                if (!a.gated) a.act[(size_t)pr * a.lda + n] = gelu_erf_f(acc[i][j]);
+                else if (!(j & 1)) a.act[(size_t)pr * a.lda + (n >> 1)] = silu_f(acc[i][j]) * acc[i][j + 1];      // columns (2m, 2m + 1) = (gate_m, up_m)
+            } else a.y[(size_t)pr * a.ldy + n] = acc[i][j];
         }
     }
 }
@@ -697,7 +788,7 @@ __global__ void moe_combine_kernel(MoeArgs a, int y_sorted) {
         const int pr = r * a.top + k, row = y_sorted ? a.inv[pr] : pr;
         s = fmaf(a.sel_w[pr], a.y[(size_t)row * a.ldy + c], s);
     }
-    a.x[(size_t)r * a.ldx + c] += s;
+    a.x[(size_t)r * a.ldx + c] += a.out_scale ? a.out_scale[c] * s : s;
 }
 __global__ void moe_gather_kernel(MoeArgs a, ActOut src, ActOut dst) {
     const int i = blockIdx.x, r = a.sorted[i] / a.top;
@@ -760,9 +851,10 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(MoeArgs a) {
     for (int k = threadIdx.x; k < ldw; k += blockDim.x) xs[k] = k < K ? x[k] : 0.f;
     __syncthreads();
     const bf16* Wt = UP ? a.up[e] : a.down[e];
+    float pair[2] = {0.f, 0.f};
     for (int rr = 0; rr < 2; ++rr) {
         const int n = blockIdx.x * 16 + warp * 2 + rr;
-        if (n >= N) continue;
+        if (n >= (UP && a.gated ? 2 * N : N)) continue;
         const uint4* w8 = reinterpret_cast<const uint4*>(Wt + (size_t)n * ldw);
         float acc = 0.f;
         for (int k = lane; k < ldw / 8; k += 32) {
@@ -772,10 +864,16 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(MoeArgs a) {
             acc = fmaf(bf16lo(ww.z), xx[4], acc); acc = fmaf(bf16hi(ww.z), xx[5], acc); acc = fmaf(bf16lo(ww.w), xx[6], acc); acc = fmaf(bf16hi(ww.w), xx[7], acc);
         }
         acc = warp_sum(acc);
+        pair[rr] = acc;
         if (lane == 0) {
-            if (UP) a.act[(size_t)pr * a.lda + n] = gelu_erf_f(acc);
+            if (UP) { if (!a.gated) a.act[(size_t)pr * a.lda + n] = gelu_erf_f(acc); }
             else a.y[(size_t)pr * a.ldy + n] = acc;
         }
+    }
+    // gated experts: the warp's two rows are (gate_m, up_m), m = blockIdx.x * 8 + warp
+    if (UP && a.gated && lane == 0) {
+        const int m = blockIdx.x * 8 + warp;
+        if (m < N) a.act[(size_t)pr * a.lda + m] = silu_f(pair[0]) * pair[1];
     }
 }
 
@@ -805,16 +903,32 @@ int gather_rows_launch(cudaStream_t st, const float* src, int lds, const int* ro
     gather_rows_kernel<<<R, 128, 0, st>>>(src, lds, rows, W, dst, ldd);
     return last_err();
 }
-int linear_f32_launch(cudaStream_t st, const float* A, int lda, const bf16* W, int ldw, int M, int N, int K, int mode, float* C, int ldc) {
+int linear_f32_launch(cudaStream_t st, const float* A, int lda, const bf16* W, int ldw, int M, int N, int K, int mode, float* C, int ldc,
+                      const float* col_scale) {
     if (M <= 0 || N <= 0 || K <= 0) return -1000;
     const dim3 grid((N + 63) / 64, (M + 63) / 64);
-    if (mode == LIN_RESID) linear_f32_kernel<LIN_RESID><<<grid, 256, 0, st>>>(A, lda, W, ldw, M, N, K, C, ldc);
-    else linear_f32_kernel<LIN_STORE><<<grid, 256, 0, st>>>(A, lda, W, ldw, M, N, K, C, ldc);
+    if (mode == LIN_RESID) linear_f32_kernel<LIN_RESID><<<grid, 256, 0, st>>>(A, lda, W, ldw, M, N, K, C, ldc, col_scale);
+    else linear_f32_kernel<LIN_STORE><<<grid, 256, 0, st>>>(A, lda, W, ldw, M, N, K, C, ldc, nullptr);
+    return last_err();
+}
+int rms_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, float eps, const float* w1, const ActOut& out1,
+                    const float* w2, const ActOut& out2) {
+    rms_rows_kernel<<<R, 256, 0, st>>>(x, ldx, rows, W, eps, w1, out1, w2, out2);
+    return last_err();
+}
+int store_rows_launch(cudaStream_t st, const float* src, int lds, int T, int W, const ActOut& dst, int col0) {
+    store_rows_kernel<<<T, 128, 0, st>>>(src, lds, W, dst, col0);
+    return last_err();
+}
+int silu_glu_launch(cudaStream_t st, const float* gu, int ld, int T, int F, const ActOut& out) {
+    silu_glu_kernel<<<dim3((F + 127) / 128, T), 128, 0, st>>>(gu, ld, F, out);
     return last_err();
 }
 int attn_prep_launch(cudaStream_t st, const RaggedBatch& rb, const AttnPrepArgs& a) {
-    if (a.kv_f32) attn_prep_kernel<float><<<rb.T, 256, 0, st>>>(rb, a);
-    else attn_prep_kernel<bf16><<<rb.T, 256, 0, st>>>(rb, a);
+    if (a.rot_dims < 0 || (a.rot_dims & 1) || a.rot_dims > a.d || a.rot_dims > 4096) return -1000;
+    const size_t sm = (size_t)a.rot_dims * sizeof(float);
+    if (a.kv_f32) attn_prep_kernel<float><<<rb.T, 256, sm, st>>>(rb, a);
+    else attn_prep_kernel<bf16><<<rb.T, 256, sm, st>>>(rb, a);
     return last_err();
 }
 template <typename KT, int REP>
@@ -895,6 +1009,7 @@ int clamped_glu_launch(cudaStream_t st, const float* gu, int ld, int stride, int
 }
 int moe_route_launch(cudaStream_t st, const MoeArgs& a, const bf16* w_router, int ldw) {
     if (a.E > 256 || a.top > a.E || a.top < 1) return -1000;
+    if (a.n_groups > 1 && (a.E % a.n_groups || a.keep < 1 || a.keep > a.n_groups || a.top > a.keep * (a.E / a.n_groups))) return -1000;
     int e;
     if (a.T <= 64) {          // few rows: logits + selection in one launch
         route_rows_kernel<<<a.T, 256, 0, st>>>(a, w_router, ldw);
@@ -910,14 +1025,14 @@ int moe_route_launch(cudaStream_t st, const MoeArgs& a, const bf16* w_router, in
 }
 int moe_experts_launch(cudaStream_t st, const MoeArgs& a) {
     if (a.T * a.top <= 32 && (a.ldwu & 255) == 0 && (a.ldwd & 255) == 0 && (size_t)std::max(a.ldwu, a.ldwd) * 4 <= 48 * 1024) {
-        moe_gemv_kernel<true><<<dim3((a.F + 15) / 16, a.T * a.top), 256, (size_t)a.ldwu * 4, st>>>(a);
+        moe_gemv_kernel<true><<<dim3(((a.gated ? 2 * a.F : a.F) + 15) / 16, a.T * a.top), 256, (size_t)a.ldwu * 4, st>>>(a);
         int e = last_err();
         if (e) return e;
         moe_gemv_kernel<false><<<dim3((a.W + 15) / 16, a.T * a.top), 256, (size_t)a.ldwd * 4, st>>>(a);
         if ((e = last_err())) return e;
         return moe_combine_launch(st, a, false);
     }
-    moe_linear_kernel<true><<<dim3((a.F + 63) / 64, a.max_tiles), 256, 0, st>>>(a);
+    moe_linear_kernel<true><<<dim3(((a.gated ? 2 * a.F : a.F) + 63) / 64, a.max_tiles), 256, 0, st>>>(a);
     int e = last_err();
     if (e) return e;
     moe_linear_kernel<false><<<dim3((a.W + 63) / 64, a.max_tiles), 256, 0, st>>>(a);

@@ -1,11 +1,13 @@
 // Kernels for models that run a RAGGED BATCH per step: the rows of one step are portions of several sequences (a prompt
 // chunk of one beside single decoded tokens of others), concatenated, with per-row and per-entry descriptors in device memory.
 // Every mechanism takes its constants as arguments so that any layer-list model can be assembled from them:
-//   Dynamic-Tanh norm, unit-RMS QK norm with a position-dependent query temperature, paged softmax attention with a sink term
+//   Dynamic-Tanh norm, RMS norm with up to two weights on one statistic, RMS QK norm (weightless or weighted) with a
+//   position-dependent query temperature and / or an interleaved-pair rotation of the leading dimensions, paged softmax attention
+//   with a sink term, an optional sliding window and an optional sigmoid output gate
 //   (any key width, any value width, grouped queries, keys / values optionally owned by another layer), the Mamba-2 mixer
 //   (causal depthwise convolution with carried window, selective state-space scan with carried f32 state, gated grouped RMS
-//   norm), a clamped gated feed-forward, and a softmax-routed mixture of experts (router, counting sort, grouped linears,
-//   ordered combine).  See ragged.cu.
+//   norm), a clamped gated feed-forward, and a mixture of experts (softmax or sigmoid scores, a selection bias, group-limited
+//   choice, plain or gated experts; router, counting sort, grouped linears, ordered combine with a per-column scale).  See ragged.cu.
 #pragma once
 
 #include "common.cuh"
@@ -34,14 +36,28 @@ int embed_scale_rows_launch(cudaStream_t st, const int* ids, int T, const bf16* 
 // out[r, c] = tanh(alpha * x[src(r), c]) * w[c] + b[c];  rows = gather list (nullptr: identity)
 int dyt_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, const float* alpha, const float* w,
                     const float* b, const ActOut& out);
-// C[M, N] (+)= A[M, K] f32 x W[N, K]^T bf16, every product and sum in f32 (no tensor cores): the exact mode's linear, and the router's
-int linear_f32_launch(cudaStream_t st, const float* A, int lda, const bf16* W, int ldw, int M, int N, int K, int mode, float* C, int ldc);
+// out_k[r, c] = x[src(r), c] / sqrt(mean_c(x^2) + eps) * w_k[c] for k = 1 and (optionally) 2: two norms of the same row share its
+// statistic.  w_k holds the final multipliers (a weight stored around zero is registered as 1 + w).
+int rms_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, float eps, const float* w1, const ActOut& out1,
+                    const float* w2, const ActOut& out2);
+// dst[r, col0 + c] = src[r, c] for c < W, in every form dst carries (f32 rows, bf16 planes)
+int store_rows_launch(cudaStream_t st, const float* src, int lds, int T, int W, const ActOut& dst, int col0);
+// C[M, N] (+)= A[M, K] f32 x W[N, K]^T bf16, every product and sum in f32 (no tensor cores): the exact mode's linear, and the router's.
+// col_scale (LIN_RESID only, nullable): C[m, n] += col_scale[n] * acc
+int linear_f32_launch(cudaStream_t st, const float* A, int lda, const bf16* W, int ldw, int M, int N, int K, int mode, float* C, int ldc,
+                      const float* col_scale = nullptr);
+// out[r, j] = silu(gu[r, 2j]) * gu[r, 2j + 1]  (interleaved (gate, up) pairs)
+int silu_glu_launch(cudaStream_t st, const float* gu, int ld, int T, int F, const ActOut& out);
 
 struct AttnPrepArgs {
     const float* qkv; int ld;         // [T, ld]: q heads | k heads | v heads (k / v absent when has_kv == 0)
     int H, G, d, dv;
     float eps;
     float temp_coef; int temp_every;  // temp_every <= 0: no query temperature
+    const float* q_norm_w;            // [d] weights of the RMS norm of queries / keys, shared by the heads; nullptr = weightless
+    const float* k_norm_w;
+    int rot_dims;                     // > 0: after the norm, dimensions (2i, 2i + 1), i < rot_dims / 2, of q and k turn by pos * rot_freq[i]
+    const double* rot_freq;           // [rot_dims / 2] radians per position (the angle and its sine / cosine are taken in 64-bit)
     ActOut q_out;                     // [T, H * d] normalised, temperature applied (f32 for sink_attention, planes for the flash kernel)
     void* k_pool; void* v_pool;       // pages [n_pages, G, KV_PAGE, d | dv] of f32, or of bf16 with an optional low-order plane
     int kv_f32; long long kv_lo_off;  // bf16 pages: element offset of the plane holding bf16(x - bf16(x)), 0 = none
@@ -57,6 +73,8 @@ struct SinkAttnArgs {
     int H, G, d, dv;
     float scale;
     const float* sink;                // [H] or nullptr (no sink term)
+    int window;                       // > 0: row i sees keys j with 0 <= i - j < window; 0: every earlier key
+    const float* gate; int ldg;       // nullable [T, ldg]: out[r, h * dv + c] *= sigmoid(gate[r, h * dv + c])
     ActOut out;                       // [T, H * dv]
     float* part; int nsplit;          // scratch [T, H, nsplit, dv + 2] when nsplit > 1
 };
@@ -103,7 +121,13 @@ struct MoeArgs {
     int* offs;                        // [E + 1] first place of each expert's pairs in `sorted`
     float* act; int lda;              // [T * top, lda]
     float* y; int ldy;                // [T * top, ldy]
-    float* x; int ldx;                // residual, += sum_k w_k y_k
+    float* x; int ldx;                // residual, += out_scale * sum_k w_k y_k
+    // selection: scores = softmax(logits) (score_fn 0) or sigmoid(logits) (1); the `top` experts with the largest score + correction
+    // are chosen among the `keep` best of `n_groups` equal groups of neighbouring experts (a group's rank: the sum of its two largest
+    // score + correction); the weights are the chosen experts' scores without the correction.  n_groups <= 1: no group limit.
+    int score_fn = 0; const float* correction = nullptr; int n_groups = 0, keep = 0;
+    int gated = 0;                    // 1: up[e] is [2F, ldwu] with (gate_j, up_j) rows interleaved, act = silu(gate) * up; 0: act = gelu_erf(up)
+    const float* out_scale = nullptr; // [W] per-column factor of the combined output (nullptr: 1)
 };
 // router logits (f32 products: a.h x w_router^T -> a.router_logits), softmax + top-k, then the counting sort by expert
 int moe_route_launch(cudaStream_t st, const MoeArgs& a, const bf16* w_router, int ldw);
