@@ -465,6 +465,111 @@ def bench_fosovik(args, rank, world, local_rank):
     print(json.dumps(out))
 
 
+def bench_gavipel(args, rank, world, local_rank):
+    """The Gavipel layer-list decoder (windowed gated attention + group-limited SiLU experts + a shared expert, a span of layers run
+    twice) beside the closest existing model, a Fosovik stack of sink-attention layers with erf-GELU experts, at equal width, layer
+    runs, heads and experts, at two sizes.  One request = 4096-token prefill + 256 greedy tokens through `crane_b200_generate_greedy`;
+    random bf16 blocks as weights (timing only; the routers are drawn properly so that the experts share the rows); one GPU."""
+    import crane_b200
+    sys.path.insert(0, os.path.join(ROOT, "tools"))
+    import bench_configs as bc
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has no model of this design"}))
+        return
+    if rank != 0:
+        return
+    S, n_dec = 4096, 256
+    peaks = load_peaks()
+    sampler = ClockSampler(0)
+    sizes = {
+        "w1024_12runs_8x896_top4": dict(
+            gav=synth.gavipel_config(width=1024, layers=8, loop=(2, 6, 2), heads=8, kv_heads=2, dim=128, window=1024, experts=8, top=4, expert_ff=896,
+                                     groups=(4, 3), shared_ff=896),
+            fsv=synth.fosovik_config(width=1024, vocab=65536, blocks=12, attn_every=1, heads=8, kv_heads=2, dim=128, moe=(8, 4, 896))),
+        "w2048_10runs_16x1024_top4": dict(
+            gav=synth.gavipel_config(width=2048, layers=6, loop=(1, 5, 2), heads=16, kv_heads=4, dim=128, window=2048, experts=16, top=4, expert_ff=1024,
+                                     groups=(4, 2), shared_ff=2048),
+            fsv=synth.fosovik_config(width=2048, vocab=65536, blocks=10, attn_every=1, heads=16, kv_heads=4, dim=128, moe=(16, 4, 1024))),
+    }
+
+    def load(cls, cfg):
+        m = cls(cfg, device=0, max_tokens=S + n_dec + 128, max_batch=4)
+        for name, shape, kind in synth.tensor_specs(cfg):
+            m.load_tensor(name, synth.make_tensor(name, shape, kind) if name.endswith("mlp.router") else bc.cheap(shape, kind))
+        m.finalize()
+        return m
+
+    def measure(m, cfg, tag):
+        ids = synth.synth_token_ids(S, cfg["vocab"], tag)
+
+        def request():
+            m.clear_kv_cache()
+            t0 = time.perf_counter()
+            out = m.generate_greedy(ids, n_dec + 1)
+            wall = time.perf_counter() - t0
+            t = m.last_timing()
+            return wall, t["prefill_ms"], t["decode_ms"], len(out) - 1
+        for _ in range(max(args.warmup, 3)):
+            request()
+        l0 = m.kernel_launches()
+        rs = [request() for _ in range(args.steps)]
+        launches = m.kernel_launches() - l0
+        # algorithmic work: every matrix a token touches once (its `top` experts of E), keys / values inside the window (hi + lo planes)
+        runs = cfg["layers"]
+        if cfg.get("loop"):
+            lp = cfg["loop"]
+            runs = cfg["layers"][:lp["start"]] + cfg["layers"][lp["start"]:lp["stop"]] * lp["times"] + cfg["layers"][lp["stop"]:]
+        W, V = cfg["width"], cfg["vocab"]
+        per_tok = V * W + (2 * W * W * cfg["loop"]["times"] if cfg.get("loop") else 0)
+        attn_fl, kv_b = 0.0, 0.0
+        for L in runs:
+            a, f = L["mixer"], L["mlp"]
+            H, G, d = a["heads"], a["kv_heads"], a["dim"]
+            gate = H * d if cfg["architecture"] == "Gavipel" else 0
+            per_tok += W * (H * d + 2 * G * d + gate) + W * H * d
+            mats = 3 if cfg["architecture"] == "Gavipel" else 2
+            per_tok += f["router"]["top"] * mats * f["expert"]["ff"] * W + f["router"]["experts"] * W
+            if f.get("shared"):
+                per_tok += 3 * f["shared"]["ff"] * W
+            win = (a.get("mask") or {}).get("size") or (1 << 30)
+            seen = sum(min(i + 1, win) for i in range(0, S, 64)) * 64                  # keys seen over the prompt's rows (per 64-row tile)
+            attn_fl += 4.0 * seen * H * d
+            kv_b += min(S + n_dec / 2, win) * 2 * G * d * 4
+        fl = 2.0 * (per_tok - V * W) * S + attn_fl + 2.0 * V * W
+        by = 2.0 * per_tok + kv_b
+        dec_s, ntok, pre_s = sum(r[2] for r in rs) / 1e3, sum(r[3] for r in rs), sum(r[1] for r in rs) / 1e3
+        return {"decode_tok_s": ntok / dec_s, "decode_us_per_step": 1e6 * dec_s / ntok, "prefill_ms": 1e3 * pre_s / len(rs),
+                "prefill_tok_s": S * len(rs) / pre_s, "prefill_tflops": fl * len(rs) / pre_s / 1e12,
+                "prefill_frac_of_bf16_peak": fl * len(rs) / pre_s / 1e12 / peaks["bf16_tflops"],
+                "decode_hbm_gbs": by / (dec_s / ntok) / 1e9, "decode_roofline_frac": by / (dec_s / ntok) / 1e9 / peaks["hbm_gbs"],
+                "algorithmic_bytes_per_step": by, "prefill_flop": fl, "e2e_tok_s": ntok / sum(r[0] for r in rs), "gpu_launches": int(launches)}
+
+    variants = {}
+    sampler.start()
+    for name, pair in sizes.items():
+        variants[name] = {}
+        for key, cls in (("gavipel", crane_b200.GavipelModel), ("closest_model_fosovik", crane_b200.FosovikModel)):
+            cfg = pair["gav" if key == "gavipel" else "fsv"]
+            m = load(cls, cfg)
+            variants[name][key] = measure(m, cfg, name + key)
+            m.close()
+    clocks = sampler.summary()
+    d = variants["w1024_12runs_8x896_top4"]["gavipel"]
+    out = {"metric": "decode_tok_per_s", "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": f"Gavipel layer-list decoder (width 1024, 8 layers of which 4 run twice, window 1024, 8 experts x 896 + shared), {S}-token prefill + {n_dec} greedy decode tokens per request; the closest existing model at equal size beside it",
+                      "weights": "random bf16 blocks (timing only)", "l2": "per-token weight stream > 126 MB L2", "parallelism": "1 GPU",
+                      "precision": os.environ.get("CRANE_B200_PRECISION", "split")},
+           "value": d["decode_tok_s"], "ms_per_step": 1e3 / d["e2e_tok_s"] * n_dec, "prefill_ms": d["prefill_ms"], "prefill_tflops": d["prefill_tflops"],
+           "e2e": {"value": d["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": int(S * 4), "d2h_bytes_per_step": int((n_dec + 1) * 4),
+                   "api": "crane_b200_generate_greedy (host prompt ids in, host token ids out; prefill inside the timed region)"},
+           "gpu_launches": d["gpu_launches"], "clocks": clocks, "variants": variants,
+           "roofline": {"bound": "hbm", "achieved": d["decode_hbm_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": d["decode_roofline_frac"],
+                        "peak_source": peaks["source"], "launch": "one decode step (graph replay): the token's weights once + keys / values inside the windows"}}
+    print(json.dumps(out))
+
+
 def other_config_summary(config, steps=2, timeout_s=120):
     """One more BASELINE config measured by THIS script in a child process (`bench.py --config <config>`), condensed for the headline
     line's `other_configs` field.  A child, so that nothing it does -- a failure, a hang (killed at the timeout) -- can keep the
@@ -493,7 +598,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="crane_b200", choices=["crane_b200", "reference"])
-    ap.add_argument("--config", default="qwen3_vl_2b", choices=["qwen3_vl_2b", "tiny", "qwen3_8b_q4km", "qwen3_5_0_8b", "fosovik"])
+    ap.add_argument("--config", default="qwen3_vl_2b", choices=["qwen3_vl_2b", "tiny", "qwen3_8b_q4km", "qwen3_5_0_8b", "fosovik", "gavipel"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the config-2 (Qwen3.5-0.8B) child measurement appended to the headline line")
     args = ap.parse_args()
@@ -507,6 +612,8 @@ def main():
         return bench_config2(args, rank, world, local_rank)
     if args.config == "fosovik":
         return bench_fosovik(args, rank, world, local_rank)
+    if args.config == "gavipel":
+        return bench_gavipel(args, rank, world, local_rank)
     cfg = synth.QWEN3_VL_2B if args.config == "qwen3_vl_2b" else synth.TINY_QWEN3_VL
     name = "Qwen3-VL-2B" if args.config == "qwen3_vl_2b" else "tiny-Qwen3-VL"
     workload = f"{name} bf16, 1x(448x448) image + {N_TEXT}-tok prompt, prefill + {N_DECODE} greedy decode tokens per request"

@@ -392,9 +392,60 @@ def fosovik_tensor_specs(cfg: dict):
     yield "head", (V, W), "linear"
 
 
+def gavipel_config(width=1024, vocab=65536, layers=8, loop=(2, 6, 2), heads=8, kv_heads=2, dim=128, window=1024, rot_dims=64,
+                   experts=8, top=4, expert_ff=896, groups=(4, 3), shared_ff=896):
+    """`layers` windowed-attention layers, each with a mixture of SiLU-gated experts and a shared expert; layers loop[0] .. loop[1]-1
+    run loop[2] times.  Sizes resemble one block of a mid-sized model so that kernels run at realistic shapes."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
+           "rot": {"base": 500000.0, "dims": rot_dims, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "groups": {"count": groups[0], "keep": groups[1]}},
+           "shared": {"ff": shared_ff}}
+    return {"architecture": "Gavipel", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "layers": [{"type": "attention", "mixer": dict(att), "mlp": dict(mlp)} for _ in range(layers)],
+            "loop": {"start": loop[0], "stop": loop[1], "times": loop[2]}}
+
+
+def gavipel_tensor_specs(cfg: dict):
+    """(name, shape, kind): 'embed', 'loop.in', 'final.norm', 'l<i>.norm1|norm2|ls1|ls2', 'l<i>.mix.q|k|v|g|o|q.norm|k.norm',
+    'l<i>.mlp.e<j>.gate|up|down', 'l<i>.mlp.router|correction', 'l<i>.mlp.shared.gate|up|down'."""
+    W, V = cfg["width"], cfg["vocab"]
+    yield "embed", (V, W), "embed"
+    yield "loop.in", (W, 2 * W), "linear"
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        H, G, d, dv = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m.get("vdim", m["dim"])
+        yield p + "norm1", (W,), "norm0"
+        yield p + "ls1", (W,), "norm"
+        yield p + "mix.q", (H * d, W), "linear"
+        yield p + "mix.k", (G * d, W), "linear"
+        yield p + "mix.v", (G * dv, W), "linear"
+        yield p + "mix.q.norm", (d,), "norm"
+        yield p + "mix.k.norm", (d,), "norm"
+        yield p + "mix.g", (H * dv, W), "linear"
+        yield p + "mix.o", (W, H * dv), "linear"
+        f = L.get("mlp")
+        if f:
+            yield p + "norm2", (W,), "norm0"
+            yield p + "ls2", (W,), "norm"
+            for e in range(f["router"]["experts"]):
+                yield f"{p}mlp.e{e}.gate", (f["expert"]["ff"], W), "linear"
+                yield f"{p}mlp.e{e}.up", (f["expert"]["ff"], W), "linear"
+                yield f"{p}mlp.e{e}.down", (W, f["expert"]["ff"]), "linear"
+            yield p + "mlp.router", (f["router"]["experts"], W), "linear"
+            yield p + "mlp.correction", (f["router"]["experts"],), "bias"
+            if f.get("shared"):
+                yield p + "mlp.shared.gate", (f["shared"]["ff"], W), "linear"
+                yield p + "mlp.shared.up", (f["shared"]["ff"], W), "linear"
+                yield p + "mlp.shared.down", (W, f["shared"]["ff"]), "linear"
+    yield "final.norm", (W,), "norm0"
+
+
 def tensor_specs(cfg: dict):
     if cfg.get("architecture") == "Fosovik":
         yield from fosovik_tensor_specs(cfg)
+        return
+    if cfg.get("architecture") == "Gavipel":
+        yield from gavipel_tensor_specs(cfg)
         return
     if cfg.get("model_type") == "qwen3_tts":
         yield from qwen3_tts_tensor_specs(cfg)
