@@ -389,6 +389,60 @@ def test_wide_heads_and_many_rows_take_the_tensor_core_paths():
     m.close()
 
 
+def random_config(seed):
+    """A layer list drawn at random: every grouping of query heads, widths that are and are not multiples of 8, windows around
+    tile and page sizes, rotation of none / some / all dimensions, every shape of expert choice, every form of repeated span."""
+    r = np.random.default_rng(seed)
+    pick = lambda *xs: xs[int(r.integers(len(xs)))]
+    layers = []
+    for _ in range(int(r.integers(1, 5))):
+        g, rep = pick(1, 2, 3), pick(1, 2, 3, 5)
+        d, dv = (64, 64) if r.random() < 0.3 else (pick(16, 18, 24, 40, 66), pick(8, 20, 24, 64, 70))
+        rot = pick(0, 2, d // 2 * 2, (d // 4) * 2)
+        mx = mixer(heads=g * rep, kv_heads=g, dim=d, vdim=dv, scale=float(pick(0.5, 1.0, 2.0)) / math.sqrt(d), window=pick(0, 1, 5, 31, 32, 33, 64, 100),
+                   rot_dims=rot, base=float(pick(50.0, 1e4)), scaling=bool(r.integers(2)))
+        f = None
+        if r.random() < 0.75:
+            E, count = pick((4, 2), (6, 3), (8, 4), (9, 1), (5, 5), (12, 3))
+            keep = int(r.integers(1, count + 1))
+            top = int(r.integers(1, keep * (E // count) + 1))
+            f = moe(ff=pick(12, 30, 64), experts=E, top=top, count=count, keep=keep, shared=pick(0, 20, 64))
+        layers.append(layer(mx, f))
+    n = len(layers)
+    loop = None
+    if r.random() < 0.8:
+        a = int(r.integers(0, n)); b = int(r.integers(a + 1, n + 1))
+        loop = (a, b, pick(1, 2, 3))
+    return config(layers, loop=loop, width=pick(72, 100, 136, 160), vocab=pick(90, 211, 300), scale=float(pick(1.0, 6.0)), eps=float(pick(1e-6, 1e-5)))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(10))
+def test_random_layer_lists(seed):
+    cfg = random_config(100 + seed)
+    r = np.random.default_rng(seed)
+    ids, other = tokens(150, cfg["vocab"], 200 + seed), tokens(70, cfg["vocab"], 300 + seed)
+    for precision, tol in (("f32", F32_TOL), ("split", SPLIT_TOL)):
+        m, w = make(cfg, 400 + seed, precision=precision)
+        want, want2 = oracle_logits(cfg, w, ids), oracle_logits(cfg, w, other)
+        assert rel(m.step_batch([(0, ids, all_rows(150))]), want) < tol, (precision, "whole")
+        m.clear_kv_cache()
+        s1 = m.seq_create()
+        at, at2, rows, rows2 = 0, 0, [], []
+        while at < 150:                                      # random cuts, the second request beside some of them
+            c = int(min(150 - at, r.choice([1, 2, 3, 17, 40, 64])))
+            entries = [(0, ids[at:at + c], all_rows(c))]
+            c2 = int(min(70 - at2, r.choice([0, 1, 2, 30])))
+            if c2:
+                entries.append((s1, other[at2:at2 + c2], all_rows(c2)))
+            lg = m.step_batch(entries)
+            rows.append(lg[:c]); rows2.append(lg[c:]); at += c; at2 += c2
+        assert rel(np.concatenate(rows), want) < tol, (precision, "cuts")
+        got2 = np.concatenate(rows2)
+        assert rel(got2, want2[:len(got2)]) < tol, (precision, "beside")
+        m.close()
+
+
 @pytest.mark.gpu
 def test_model_folder_loader_and_trace_runner(tmp_path):
     import json, os, subprocess, sys
