@@ -613,6 +613,54 @@ __global__ void silu_glu_kernel(const float* __restrict__ gu, int ld, int F, Act
     store_act(out, r, j, silu_f(gu[(size_t)r * ld + 2 * j]) * gu[(size_t)r * ld + 2 * j + 1]);
 }
 
+// Router logits of one row by one warp: NB experts at a time share the loads of the f32 row; a lane owns 8 neighbouring columns per
+// 256-column step (one 16-byte load of each bf16 weight row, two of the f32 row), sums them in column order into one accumulator
+// per expert, and the lanes meet in warp_sum's tree -- the same order for every row, few or many in the step.  `vec` = the width
+// and the leading dimensions allow the 16-byte loads; otherwise lanes stride single columns.
+template <int NB>
+__device__ __forceinline__ void router_dots(const float* __restrict__ h, const bf16* __restrict__ w, int ldw, int W, int ne, int lane, bool vec, float* out) {
+    float acc[NB];
+#pragma unroll
+    for (int i = 0; i < NB; ++i) acc[i] = 0.f;
+    if (vec) {
+        for (int k = lane * 8; k < W; k += 256) {
+            const float4 x0 = *reinterpret_cast<const float4*>(h + k), x1 = *reinterpret_cast<const float4*>(h + k + 4);
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                if (i < ne) {
+                    const uint4 ww = *reinterpret_cast<const uint4*>(w + (size_t)i * ldw + k);
+                    float a = acc[i];
+                    a = fmaf(bf16lo(ww.x), x0.x, a); a = fmaf(bf16hi(ww.x), x0.y, a); a = fmaf(bf16lo(ww.y), x0.z, a); a = fmaf(bf16hi(ww.y), x0.w, a);
+                    a = fmaf(bf16lo(ww.z), x1.x, a); a = fmaf(bf16hi(ww.z), x1.y, a); a = fmaf(bf16lo(ww.w), x1.z, a); a = fmaf(bf16hi(ww.w), x1.w, a);
+                    acc[i] = a;
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < W; k += 32) {
+            const float x = h[k];
+#pragma unroll
+            for (int i = 0; i < NB; ++i) if (i < ne) acc[i] = fmaf(x, __bfloat162float(w[(size_t)i * ldw + k]), acc[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NB; ++i) out[i] = warp_sum(acc[i]);
+}
+__device__ __forceinline__ bool router_vec_ok(int W, int ldw, int ldh) { return (W & 7) == 0 && (ldw & 7) == 0 && (ldh & 3) == 0; }
+
+// Many rows: one warp per row, four experts per pass over the row (which stays in L1).
+__global__ void __launch_bounds__(256) router_logits_kernel(MoeArgs a, const bf16* __restrict__ w_router, int ldw) {
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= a.T) return;
+    const float* h = a.h + (size_t)r * a.ldh;
+    const bool vec = router_vec_ok(a.W, ldw, a.ldh);
+    for (int e0 = 0; e0 < a.E; e0 += 4) {
+        float z[4];
+        router_dots<4>(h, w_router + (size_t)e0 * ldw, ldw, a.W, min(4, a.E - e0), lane, vec, z);
+        if (lane < min(4, a.E - e0)) a.router_logits[(size_t)r * a.ldr + e0 + lane] = lane == 0 ? z[0] : lane == 1 ? z[1] : lane == 2 ? z[2] : z[3];
+    }
+}
+
 // Expert choice for one row by one warp.  z: the row's router logits; sc / ch / gs: 256 floats each of this warp's scratch.
 // Scores = softmax over all experts or element-wise sigmoid; the choice value adds the selection bias; with n_groups > 1 only the
 // experts of the `keep` groups with the largest (sum of the two largest choice values) stay eligible -- the others count as
@@ -690,11 +738,10 @@ __global__ void __launch_bounds__(256) route_rows_kernel(MoeArgs a, const bf16* 
     __shared__ float scr[3][256];
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* h = a.h + (size_t)r * a.ldh;
+    const bool vec = router_vec_ok(a.W, ldw, a.ldh);
     for (int e = warp; e < a.E; e += 8) {
-        const bf16* wr = w_router + (size_t)e * ldw;
-        float acc = 0.f;
-        for (int k = lane; k < a.W; k += 32) acc = fmaf(h[k], __bfloat162float(wr[k]), acc);
-        acc = warp_sum(acc);
+        float acc;
+        router_dots<1>(h, w_router + (size_t)e * ldw, ldw, a.W, 1, lane, vec, &acc);
         if (lane == 0) { z[e] = acc; a.router_logits[(size_t)r * a.ldr + e] = acc; }
     }
     __syncthreads();
@@ -1015,7 +1062,8 @@ int moe_route_launch(cudaStream_t st, const MoeArgs& a, const bf16* w_router, in
         route_rows_kernel<<<a.T, 256, 0, st>>>(a, w_router, ldw);
         e = last_err();
     } else {
-        if ((e = linear_f32_launch(st, a.h, a.ldh, w_router, ldw, a.T, a.E, a.W, LIN_STORE, (float*)a.router_logits, a.ldr))) return e;
+        router_logits_kernel<<<(a.T + 7) / 8, 256, 0, st>>>(a, w_router, ldw);
+        if ((e = last_err())) return e;
         route_kernel<<<(a.T + 3) / 4, 128, 0, st>>>(a);
         e = last_err();
     }
