@@ -23,6 +23,13 @@ __device__ __forceinline__ void store_act(const ActOut& o, int r, int c, float v
     }
 }
 
+__device__ __forceinline__ void cp_async16s(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+
 // KV page elements: f32, or bf16 with an optional low-order plane `lo` elements further on (x ~= hi + lo, ~16 mantissa bits)
 template <typename KT> __device__ __forceinline__ float kv_load(const KT* p, long long lo);
 template <> __device__ __forceinline__ float kv_load<float>(const float* p, long long) { return *p; }
@@ -207,8 +214,9 @@ template <> __device__ __forceinline__ void kv_load8<bf16>(const bf16* p, long l
         v[4] += bf16lo(l.z); v[5] += bf16hi(l.z); v[6] += bf16lo(l.w); v[7] += bf16hi(l.w);
     }
 }
-template <typename KT, int REP>
+template <typename KT, int REP, bool STAGE>
 __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBatch rb, SinkAttnArgs a) {
+    constexpr bool stage = STAGE;
     extern __shared__ __align__(16) float smem[];
     const int d = a.d, dv = a.dv, rep = a.H / a.G, nb = (rep + REP - 1) / REP;
     float* sq = smem;                                   // [REP][d]
@@ -234,23 +242,57 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
         for (int c = 0; c < ATT_MAXC; ++c) acc[q][c] = 0.f;
     }
     const bool kvec = (d & 7) == 0, vvec = (dv & 7) == 0;
+    // STAGE (widths that allow 16-byte copies, room in shared memory, a small launch): a warp first brings its whole tile -- 32 key rows and
+    // 32 value rows, every plane -- into its own shared-memory patch with one burst of cp.async, so the tile costs one trip to memory
+    // instead of a dozen dependent load rounds; rows are padded by 16 bytes, which spreads a lane-per-row access over all banks.
+    // The arithmetic and its order are the same either way.
+    const int ks_e = stage ? d + 16 / (int)sizeof(KT) : d, vs_e = stage ? dv + 16 / (int)sizeof(KT) : dv;      // row strides (elements)
+    const int planes = (sizeof(KT) == 2 && a.kv_lo_off) ? 2 : 1;
+    KT* kst = nullptr; KT* vst = nullptr;
+    if (stage) {
+        KT* all = reinterpret_cast<KT*>(wa + (size_t)ATT_WARPS * REP * dv + ((4 - ((REP * d + 2 * ATT_WARPS * REP + ATT_WARPS * REP * dv) & 3)) & 3));
+        kst = all + (size_t)warp * 32 * planes * (ks_e + vs_e);
+        vst = kst + (size_t)32 * planes * ks_e;
+    }
+    const long long klo = !stage ? a.kv_lo_off : planes == 2 ? (long long)32 * ks_e : 0, vlo = !stage ? a.kv_lo_off : planes == 2 ? (long long)32 * vs_e : 0;
     for (int t = t_lo + warp; t < t_hi; t += ATT_WARPS) {
         const int j = t * 32 + lane;
         const int pg = bt[(t * 32) / KV_PAGE];           // a 32-key tile never straddles a 64-token page
         const size_t base = ((size_t)pg * a.G + g) * KV_PAGE + ((t * 32) % KV_PAGE);
+        const int cnt = min(32, nkeys - t * 32);
+        if (stage) {
+            __syncwarp();                                 // the patch's last readers are done
+            const int kc = d * (int)sizeof(KT) / 16, vc = dv * (int)sizeof(KT) / 16;      // 16-byte pieces per row
+            for (int pl = 0; pl < planes; ++pl) {
+                const KT* ksrc = (const KT*)a.k_pool + base * d + (pl ? a.kv_lo_off : 0);
+                const KT* vsrc = (const KT*)a.v_pool + base * dv + (pl ? a.kv_lo_off : 0);
+                for (int i = lane; i < cnt * kc; i += 32) {
+                    const int row = i / kc, ch = i % kc;
+                    cp_async16s(reinterpret_cast<unsigned char*>(kst + (size_t)pl * 32 * ks_e + (size_t)row * ks_e) + ch * 16,
+                                reinterpret_cast<const unsigned char*>(ksrc + (size_t)row * d) + ch * 16);
+                }
+                for (int i = lane; i < cnt * vc; i += 32) {
+                    const int row = i / vc, ch = i % vc;
+                    cp_async16s(reinterpret_cast<unsigned char*>(vst + (size_t)pl * 32 * vs_e + (size_t)row * vs_e) + ch * 16,
+                                reinterpret_cast<const unsigned char*>(vsrc + (size_t)row * dv) + ch * 16);
+                }
+            }
+            asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
+            __syncwarp();
+        }
         float sc[REP];
 #pragma unroll
         for (int q = 0; q < REP; ++q) sc[q] = 0.f;
         const bool seen = j < nkeys && j >= key0;
         if (seen) {
-            const KT* kr = (const KT*)a.k_pool + (base + lane) * d;
+            const KT* kr = stage ? kst + (size_t)lane * ks_e : (const KT*)a.k_pool + (base + lane) * d;
             if (kvec) {
                 // UN pieces of the key row are requested before the first is used: the loop is bound by memory latency, not by arithmetic
                 constexpr int UN = REP <= 2 ? 4 : 2;
                 for (int c0 = 0; c0 < d; c0 += 8 * UN) {
                     float kf[UN][8];
 #pragma unroll
-                    for (int u = 0; u < UN; ++u) if (c0 + 8 * u < d) kv_load8<KT>(kr + c0 + 8 * u, a.kv_lo_off, kf[u]);
+                    for (int u = 0; u < UN; ++u) if (c0 + 8 * u < d) kv_load8<KT>(kr + c0 + 8 * u, klo, kf[u]);
 #pragma unroll
                     for (int u = 0; u < UN; ++u) {
                         const int c = c0 + 8 * u;
@@ -287,15 +329,14 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
             for (int c = 0; c < ATT_MAXC; ++c) acc[q][c] *= corr;
             m[q] = mn;
         }
-        const int cnt = min(32, nkeys - t * 32);
-        const KT* vb = (const KT*)a.v_pool + base * dv;
+        const KT* vb = stage ? vst : (const KT*)a.v_pool + base * dv;
         if (vvec) {
             const bool mine = 8 * lane < dv;
             constexpr int VN = REP <= 2 ? 4 : 2;              // value rows in flight
             for (int j0 = 0; j0 < cnt; j0 += VN) {
                 float v[VN][8];
 #pragma unroll
-                for (int u = 0; u < VN; ++u) if (mine && j0 + u < cnt) kv_load8<KT>(vb + (size_t)(j0 + u) * dv + 8 * lane, a.kv_lo_off, v[u]);
+                for (int u = 0; u < VN; ++u) if (mine && j0 + u < cnt) kv_load8<KT>(vb + (size_t)(j0 + u) * vs_e + 8 * lane, vlo, v[u]);
 #pragma unroll
                 for (int u = 0; u < VN; ++u) {
                     const int jj = j0 + u;                    // (uniform over the warp)
@@ -433,12 +474,6 @@ __global__ void conv_window_kernel(RaggedBatch rb, Mamba2Args a, int C, int col0
 // double-buffered: chunk c + 1 is in flight while chunk c is consumed.  dt = softplus(.) and the decay exp(-exp(A) dt) are
 // computed once per token, in f32, when its chunk lands.
 constexpr int SSD_NS = 8, SSD_MAXR = 32, SSD_COLS = 16, SSD_CH = 16;      // N <= 256; 16 columns x 8 = 128 threads per block: one warp per scheduler, many blocks
-__device__ __forceinline__ void cp_async16s(void* smem_dst, const void* gsrc) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
 // Staged layout of one token: x slice [SSD_COLS] | B | C | dt, pad.  Thread ns owns the CONTIGUOUS state rows ns * R .. ns * R + R - 1,
 // so it reads its B and C values as float4; every R-run is followed by 4 pad floats, which spreads the eight runs of a warp over
 // all banks.
@@ -981,11 +1016,23 @@ int attn_prep_launch(cudaStream_t st, const RaggedBatch& rb, const AttnPrepArgs&
 template <typename KT, int REP>
 static int sink_attention_launch_t(cudaStream_t st, const RaggedBatch& rb, const SinkAttnArgs& a) {
     const int rep = a.H / a.G, nb = (rep + REP - 1) / REP;
-    const size_t smem = (size_t)(REP * a.d + 2 * ATT_WARPS * REP + ATT_WARPS * REP * a.dv) * sizeof(float);
+    size_t smem = (size_t)(REP * a.d + 2 * ATT_WARPS * REP + ATT_WARPS * REP * a.dv) * sizeof(float);
     if (smem > 200 * 1024) return -1000;
-    static SmemOptIn seen;
-    if (const int e = ensure_dyn_smem(sink_attention_kernel<KT, REP>, smem, seen)) return e;
-    sink_attention_kernel<KT, REP><<<dim3(rb.T, a.G * nb, a.nsplit), ATT_WARPS * 32, smem, st>>>(rb, a);
+    // per-warp staging patches for the key / value tiles where the widths allow 16-byte copies and the patches fit
+    const int planes = (sizeof(KT) == 2 && a.kv_lo_off) ? 2 : 1;
+    const size_t patch = (size_t)ATT_WARPS * 32 * planes * ((size_t)a.d * sizeof(KT) + 16 + (size_t)a.dv * sizeof(KT) + 16) + 16;
+    // ... and the launch is small (a decode step: about two blocks per SM at most).  A launch of thousands of blocks hides its load
+    // latency by residency instead, which the patches' shared memory would take away.
+    const int stage = ((a.d & 7) == 0 && (a.dv & 7) == 0 && smem + patch <= 200 * 1024 && (long long)rb.T * a.G * nb * a.nsplit <= 300) ? 1 : 0;
+    if (stage) smem += patch;
+    static SmemOptIn seen, seen_staged;
+    if (stage) {
+        if (const int e = ensure_dyn_smem(sink_attention_kernel<KT, REP, true>, smem, seen_staged)) return e;
+        sink_attention_kernel<KT, REP, true><<<dim3(rb.T, a.G * nb, a.nsplit), ATT_WARPS * 32, smem, st>>>(rb, a);
+        return last_err();
+    }
+    if (const int e = ensure_dyn_smem(sink_attention_kernel<KT, REP, false>, smem, seen)) return e;
+    sink_attention_kernel<KT, REP, false><<<dim3(rb.T, a.G * nb, a.nsplit), ATT_WARPS * 32, smem, st>>>(rb, a);
     return last_err();
 }
 template <typename KT>
